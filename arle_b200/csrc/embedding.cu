@@ -1,0 +1,36 @@
+// Token embedding: residual[t, :] = float32(table[ids[t], :]).
+// The residual stream is kept in 32-bit in both engine precisions, so the table
+// row is widened here once.  An id outside [0, vocab) writes zeros and raises the
+// error flag instead of reading out of bounds (the host checks ids first).
+#include "common.cuh"
+using namespace arle;
+
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int hidden, int vocab,
+                                 int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * hidden;
+  if (id < 0 || id >= vocab) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
+    if (threadIdx.x == 0 && err) atomicExch(err, 1);
+    return;
+  }
+  const T* row = table + (size_t)id * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+ARLE_API int arle_embedding(const int* ids, const void* table, int table_dtype, float* out,
+                            int num_tokens, int hidden, int vocab, int* err, cudaStream_t s) {
+  if (num_tokens <= 0) return 0;
+  if (hidden <= 0 || vocab <= 0) return ARLE_E_BADARG;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == 0)
+    embedding_kernel<float><<<num_tokens, threads, 0, s>>>(ids, (const float*)table, out, hidden, vocab, err);
+  else if (table_dtype == 1)
+    embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, err);
+  else
+    return ARLE_E_BADARG;
+  return launch_status();
+}

@@ -1,0 +1,87 @@
+// RMSNorm over the 32-bit residual stream, fused with the residual sum.
+//
+// For output row i (source row r = rows ? rows[i] : i):
+//     x      = resid[r, :] (+ delta[r, :] when delta is given)      in float32
+//     resid[r, :] = x                      (when write_resid)
+//     out[i, :]   = x * rsqrt(mean(x^2) + eps) * weight
+// The sum of squares, the inverse and the product are float32; the only rounding
+// to the activation type is the final store.  One block per row, the row staged
+// in shared memory, so the reduction order depends on the row length alone and
+// a row's result does not depend on what else is in the batch.
+#include "common.cuh"
+using namespace arle;
+
+template <typename TA>
+__global__ void rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+                               const int* __restrict__ rows, const float* __restrict__ weight,
+                               TA* __restrict__ out, int hidden, float eps, int write_resid) {
+  extern __shared__ float xs[];
+  __shared__ float red[33];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* xr = resid + (size_t)r * hidden;
+  const TA* dr = delta ? delta + (size_t)r * hidden : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float x = xr[c];
+    if (dr) x += to_f32(dr[c]);
+    xs[c] = x;
+    if (write_resid) xr[c] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  TA* o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    o[c] = from_f32<TA>(xs[c] * inv * weight[c]);
+}
+
+template <typename TA>
+static int launch(float* resid, const void* delta, const int* rows, const float* weight, void* out,
+                  int n_out, int hidden, float eps, int write_resid, cudaStream_t s) {
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel<TA>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  rmsnorm_kernel<TA><<<n_out, threads, smem, s>>>(resid, (const TA*)delta, rows, weight, (TA*)out, hidden,
+                                                  eps, write_resid);
+  return launch_status();
+}
+
+// act_dtype: type of delta and out.  The gain vector is float32 (norm gains are
+// widened once at load; they are a few KB).
+ARLE_API int arle_rmsnorm(float* resid, const void* delta, const int* rows, const float* weight,
+                          void* out, int act_dtype, int n_out, int hidden, float eps, int write_resid,
+                          cudaStream_t s) {
+  if (n_out <= 0) return 0;
+  if (hidden <= 0) return ARLE_E_BADARG;
+  if (act_dtype == 0) return launch<float>(resid, delta, rows, weight, out, n_out, hidden, eps, write_resid, s);
+  if (act_dtype == 1) return launch<__nv_bfloat16>(resid, delta, rows, weight, out, n_out, hidden, eps, write_resid, s);
+  return ARLE_E_BADARG;
+}
+
+// resid[r, :] += delta[r, :] for all rows: the residual sum alone, for a branch
+// output that no norm follows directly.
+template <typename TA>
+__global__ void residual_add_kernel(float* __restrict__ resid, const TA* __restrict__ delta, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    resid[i] += to_f32(delta[i]);
+}
+
+ARLE_API int arle_residual_add(float* resid, const void* delta, int act_dtype, int rows, int hidden, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  const size_t total = (size_t)rows * hidden;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (act_dtype == 0)
+    residual_add_kernel<float><<<(int)blocks, 256, 0, s>>>(resid, (const float*)delta, total);
+  else if (act_dtype == 1)
+    residual_add_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, s>>>(resid, (const __nv_bfloat16*)delta, total);
+  else
+    return ARLE_E_BADARG;
+  return launch_status();
+}

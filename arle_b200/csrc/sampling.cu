@@ -1,0 +1,190 @@
+// Next-token choice from float32 logits, one block per row.
+//
+// A row with temperature <= 0 or top_k == 1 is greedy: the index of the largest
+// logit, ties to the lowest index.  Otherwise
+//     p = softmax(logits / temperature)                    (float32, max-subtracted)
+//     min_p:  drop p_i < min_p * max(p)                    (0 = off)
+//     top_k:  keep the k most probable                     (<= 0 = off)
+//     top_p:  keep the most probable tokens whose mass first reaches top_p (>= 1 = off)
+// each followed by a renormalisation, then the first index, in index order, whose
+// cumulative probability exceeds u (u in [0, 1) comes from the host's generator).
+// The top_k and top_p cut-offs are found by 32 bisection steps on a probability
+// threshold, which converges to the exact set when no two probabilities tie at
+// the threshold.  The probabilities live in a caller-provided scratch row
+// [rows, vocab] of float32.
+#include "common.cuh"
+using namespace arle;
+
+constexpr int kSampleThreads = 256;
+
+__device__ __forceinline__ void block_argmax(const float* __restrict__ x, int n, float* sval, int* sidx,
+                                             int* out) {
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = x[i];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+  sval[threadIdx.x] = best;
+  sidx[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float v = sval[threadIdx.x + s];
+      const int i = sidx[threadIdx.x + s];
+      if (v > sval[threadIdx.x] || (v == sval[threadIdx.x] && i < sidx[threadIdx.x])) {
+        sval[threadIdx.x] = v;
+        sidx[threadIdx.x] = i;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *out = sidx[0] == 0x7fffffff ? 0 : sidx[0];
+}
+
+// Zero what lies below thr, renormalise the rest; returns nothing, probabilities sum to 1 after.
+__device__ __forceinline__ void cut_below(float* p, int n, float thr, float* red) {
+  float kept = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = p[i];
+    if (v < thr) p[i] = 0.f; else kept += v;
+  }
+  kept = block_sum(kept, red);
+  const float inv = 1.0f / kept;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) p[i] *= inv;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSampleThreads) sample_kernel(
+    const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
+    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+    const float* __restrict__ uniform, float* __restrict__ scratch, int* __restrict__ out) {
+  __shared__ float red[33];
+  __shared__ float sval[kSampleThreads];
+  __shared__ int sidx[kSampleThreads];
+  __shared__ int chosen_chunk;
+  const int row = blockIdx.x;
+  const float* x = logits + (size_t)row * ld;
+  const float temp = temperature ? temperature[row] : 0.f;
+  const int k = top_k ? top_k[row] : -1;
+  if (!(temp > 0.f) || k == 1) {
+    block_argmax(x, vocab, sval, sidx, out + row);
+    return;
+  }
+  float* p = scratch + (size_t)row * vocab;
+  const float inv_t = 1.0f / temp;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) mx = fmaxf(mx, x[i] * inv_t);
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float e = expf(x[i] * inv_t - mx);
+    p[i] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red);
+  const float inv_sum = 1.0f / sum;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) p[i] *= inv_sum;
+  __syncthreads();
+  float pmax = inv_sum;  // exp(0) / sum
+
+  const float mp = min_p ? min_p[row] : 0.f;
+  if (mp > 0.f) {
+    cut_below(p, vocab, mp * pmax, red);
+    float m2 = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) m2 = fmaxf(m2, p[i]);
+    pmax = block_max(m2, red);
+  }
+  if (k > 0 && k < vocab) {
+    // smallest threshold that keeps at most k entries
+    float lo = 0.f, hi = pmax;
+    for (int it = 0; it < 32; ++it) {
+      const float mid = 0.5f * (lo + hi);
+      float c = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) c += p[i] >= mid ? 1.f : 0.f;
+      c = block_sum(c, red);
+      if (c > (float)k) lo = mid; else hi = mid;
+    }
+    cut_below(p, vocab, hi, red);
+    float m2 = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) m2 = fmaxf(m2, p[i]);
+    pmax = block_max(m2, red);
+  }
+  const float tp = top_p ? top_p[row] : 1.f;
+  if (tp < 1.f) {
+    // largest threshold whose kept mass still reaches top_p
+    float lo = 0.f, hi = pmax;
+    for (int it = 0; it < 32; ++it) {
+      const float mid = 0.5f * (lo + hi);
+      float mass = 0.f;
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = p[i];
+        if (v >= mid) mass += v;
+      }
+      mass = block_sum(mass, red);
+      if (mass >= tp) lo = mid; else hi = mid;
+    }
+    cut_below(p, vocab, lo, red);
+  }
+  // inverse CDF in index order: contiguous chunk per thread, then a scan of one chunk
+  const int chunk = (vocab + blockDim.x - 1) / blockDim.x;
+  const int b = threadIdx.x * chunk, e = min(vocab, b + chunk);
+  float part = 0.f;
+  for (int i = b; i < e; ++i) part += p[i];
+  sval[threadIdx.x] = part;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int i = 0; i < (int)blockDim.x; ++i) total += sval[i];
+    const float target = uniform[row] * total;
+    float c = 0.f;
+    int pick = -1;
+    for (int i = 0; i < (int)blockDim.x; ++i) {
+      if (target < c + sval[i]) { pick = i; break; }
+      c += sval[i];
+    }
+    chosen_chunk = pick;
+    red[0] = c;       // mass before the chosen chunk
+    red[1] = target;
+  }
+  __syncthreads();
+  const int cc = chosen_chunk;
+  if (cc < 0) {
+    // rounding left u beyond the total mass: the last index with non-zero probability
+    int last = -1;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) if (p[i] > 0.f) last = max(last, i);
+    sidx[threadIdx.x] = last;
+    __syncthreads();
+    for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
+      if (threadIdx.x < s) sidx[threadIdx.x] = max(sidx[threadIdx.x], sidx[threadIdx.x + s]);
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) out[row] = max(sidx[0], 0);
+    return;
+  }
+  if (threadIdx.x == cc) {
+    float c = red[0];
+    const float target = red[1];
+    int pick = -1, last = b;
+    for (int i = b; i < e; ++i) {
+      if (p[i] > 0.f) last = i;
+      c += p[i];
+      if (target < c) { pick = i; break; }
+    }
+    out[row] = pick >= 0 ? pick : last;
+  }
+}
+
+ARLE_API int arle_sample(const float* logits, int ld, int rows, int vocab, const float* temperature,
+                         const int* top_k, const float* top_p, const float* min_p, const float* uniform,
+                         float* scratch, int* out, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || ld < vocab) return ARLE_E_BADARG;
+  if (temperature && (!uniform || !scratch)) return ARLE_E_BADARG;
+  sample_kernel<<<rows, kSampleThreads, 0, s>>>(logits, ld, vocab, temperature, top_k, top_p, min_p, uniform,
+                                                scratch, out);
+  return launch_status();
+}

@@ -1,0 +1,246 @@
+"""The kernels of the engine, as Python functions over torch tensors.
+
+Each function checks its arguments, then calls one ``extern "C"`` launcher of the
+package's CUDA library on torch's current stream.  Outputs are written into
+tensors the caller provides; nothing here allocates device memory.  There is no
+CPU path: the first call loads the library (building it when needed) and raises
+if that fails or if a tensor is not on a CUDA device.
+
+Matrix products: the float32 path uses the package's own FFMA kernel
+(``gemm_f32.cu``: true 32-bit, fixed summation order).  The bfloat16 path calls
+cuBLAS through ``torch.mm``, as cklxx/arle calls cuBLASLt for its projections
+(crates/cuda-kernels/csrc/gemm/gemv.cu:298-482).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import build as _build
+
+_LIB = None
+
+_P, _I, _F = c_void_p, c_int, c_float
+_SIGNATURES = {
+    "arle_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+    "arle_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
+    "arle_residual_add": [_P, _P, _I, _I, _I, _P],
+    "arle_silu_mul": [_P, _P, _I, _I, _I, _P],
+    "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "arle_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """The loaded CUDA library; built on first use.  Raises if it cannot be had."""
+    global _LIB
+    if _LIB is None:
+        path = _build.library_path()
+        lib = ctypes.CDLL(path)
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        _LIB = lib
+    return _LIB
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"unsupported dtype {t.dtype}: the kernels take float32 and bfloat16")
+
+
+def _ptr(t, name="tensor"):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}: arle_b200 kernels run on CUDA devices only (there is no CPU path)")
+    return t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str):
+    if code == 0:
+        return
+    if code == -2:
+        raise KernelError(f"{what}: sizes not supported by this kernel")
+    if code == -3:
+        raise KernelError(f"{what}: bad argument")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _i32(t, name):
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, got {t.dtype}")
+    return t
+
+
+# ------------------------------------------------------------------- embedding
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor = None) -> None:
+    """out[t, :] = float32(table[ids[t], :]).  ids int32 [T]; out float32 [T, H]."""
+    T, H = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError("embedding: out must be contiguous float32 and the table contiguous")
+    if ids.numel() != T or table.shape[1] != H:
+        raise KernelError(f"embedding: shapes ids {tuple(ids.shape)} table {tuple(table.shape)} out {tuple(out.shape)}")
+    _i32(ids, "ids")
+    _check(library().arle_embedding(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, table.shape[0],
+                                    _ptr(err), _stream()), "embedding")
+
+
+# ------------------------------------------------------------------------ norm
+def rmsnorm(resid, delta, rows, weight, eps: float, out, write_resid: bool) -> None:
+    """For output row i (source row r = rows[i], or i): x = resid[r] (+ delta[r]);
+    resid[r] = x when write_resid; out[i] = x * rsqrt(mean(x^2) + eps) * weight.
+    resid float32 [N, H]; delta and out in the activation type; weight float32 [H]."""
+    H = resid.shape[1]
+    n_out = out.shape[0]
+    if resid.dtype != torch.float32 or weight.dtype != torch.float32:
+        raise KernelError("rmsnorm: residual and weight must be float32")
+    if not (resid.is_contiguous() and out.is_contiguous()) or out.shape[1] != H or weight.numel() != H:
+        raise KernelError("rmsnorm: bad shapes or strides")
+    if delta is not None and (delta.dtype != out.dtype or delta.shape != resid.shape or not delta.is_contiguous()):
+        raise KernelError("rmsnorm: delta must match the residual's shape and the output's type")
+    if rows is not None:
+        _i32(rows, "rows")
+        if rows.numel() != n_out:
+            raise KernelError("rmsnorm: one output row per entry of rows")
+    elif n_out != resid.shape[0]:
+        raise KernelError("rmsnorm: output rows must match residual rows when no row list is given")
+    _check(library().arle_rmsnorm(_ptr(resid), _ptr(delta), _ptr(rows), _ptr(weight), _ptr(out), _dt(out), n_out, H,
+                                  float(eps), int(bool(write_resid)), _stream()), "rmsnorm")
+
+
+def residual_add(resid, delta) -> None:
+    """resid += delta (float32 residual, delta in the activation type)."""
+    if resid.dtype != torch.float32 or resid.shape != delta.shape or not (resid.is_contiguous() and delta.is_contiguous()):
+        raise KernelError("residual_add: residual float32, same contiguous shape as delta")
+    _check(library().arle_residual_add(_ptr(resid), _ptr(delta), _dt(delta), resid.shape[0], resid.shape[1], _stream()),
+           "residual_add")
+
+
+# ------------------------------------------------------------------------ gemm
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] . w[N, K]^T (weights stored [out_features, in_features])."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"gemm: shapes x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    if x.dtype == torch.float32:
+        if out.dtype != torch.float32 or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("gemm: the float32 path takes float32 activations with unit inner stride")
+        _check(library().arle_gemm_f32(_ptr(x), _ptr(w), _dt(w), _ptr(out), M, N, K, x.stride(0), w.stride(0),
+                                       out.stride(0), _stream()), "gemm_f32")
+        return
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm: bfloat16 path needs bfloat16 operands, got {x.dtype} and {w.dtype}")
+    _ptr(x), _ptr(w), _ptr(out)
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, w.t(), out=out)
+    elif out.dtype == torch.float32:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        raise KernelError(f"gemm: output type {out.dtype}")
+
+
+# ------------------------------------------------------------------- attention
+def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, k_cache, v_cache,
+                   nq: int, nkv: int, hd: int, page_size: int) -> None:
+    """Per-head q/k RMSNorm (weights float32 [hd] or None), rotary encoding, and the
+    store of k and v into the paged cache, in place on qkv [T, (nq + 2 nkv) hd]
+    (nkv = 0: the rows hold q only and nothing is stored)."""
+    T = qkv.shape[0]
+    if qkv.stride(1) != 1 or qkv.shape[1] < (nq + 2 * nkv) * hd:
+        raise KernelError("attention_prep: qkv must be [T, >= (nq + 2 nkv) hd] with unit inner stride")
+    if hd % 2 or hd > 256:
+        raise KernelError(f"attention_prep: head_dim {hd} not supported (even, at most 256)")
+    for w_ in (q_weight, k_weight):
+        if w_ is not None and (w_.dtype != torch.float32 or w_.numel() != hd):
+            raise KernelError("attention_prep: norm weights must be float32 [head_dim]")
+    if nkv > 0:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise KernelError("attention_prep: cache type differs from activation type")
+        if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
+            raise KernelError(f"attention_prep: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
+        if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+            raise KernelError("attention_prep: cache layers must be contiguous")
+        _i32(slot_mapping, "slot_mapping")
+    _i32(positions, "positions")
+    if rotary_dim and (inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("attention_prep: inv_freq must be float32 [rotary_dim / 2]")
+    _check(library().arle_attention_prep(
+        _ptr(qkv), _dt(qkv), qkv.stride(0), _ptr(positions), _ptr(slot_mapping), _ptr(q_weight), _ptr(k_weight),
+        float(eps), _ptr(inv_freq) if rotary_dim else None, int(rotary_dim), _ptr(k_cache) if nkv else None,
+        _ptr(v_cache) if nkv else None, nq, nkv, hd, page_size, T, _stream()), "attention_prep")
+
+
+def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_table, nq: int, nkv: int, hd: int,
+                    page_size: int, scale: float, window, batch=None) -> None:
+    """Causal attention of this step's queries over the paged cache.
+
+    q: [T, nq*hd] view (row stride free, unit inner stride); out: contiguous
+    [T, nq*hd]; caches [pages, nkv, page_size, hd]; positions / row_of_token int32
+    [T]; block_table int32 [rows, max_pages].  ``window`` None or <= 0 means all
+    keys.  ``batch`` (a StepContext) lets faster kernels pick their launch shape;
+    the general kernel does not need it."""
+    T = q.shape[0]
+    if q.stride(1) != 1 or q.shape[1] != nq * hd or out.shape != (T, nq * hd) or not out.is_contiguous():
+        raise KernelError("paged_attention: q must be [T, nq*hd] with unit inner stride and out contiguous [T, nq*hd]")
+    if q.dtype != k_cache.dtype or out.dtype != q.dtype:
+        raise KernelError("paged_attention: q, out and cache must share a type")
+    if hd > 256 or nq % nkv:
+        raise KernelError(f"paged_attention: head_dim {hd} / heads {nq}:{nkv} not supported")
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError(f"paged_attention: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
+    _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _i32(block_table, "block_table")
+    if block_table.stride(1) != 1:
+        raise KernelError("paged_attention: block table rows must be contiguous")
+    _check(library().arle_paged_attention_plain(
+        _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), _ptr(positions), _ptr(row_of_token),
+        _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
+        int(window) if window else 0, T, _stream()), "paged_attention")
+
+
+# ------------------------------------------------------------------ activation
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up [T, 2I], out [T, I]."""
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype != out.dtype:
+        raise KernelError("silu_mul: gate_up must be contiguous [T, 2I] and out contiguous [T, I] of one type")
+    _check(library().arle_silu_mul(_ptr(gate_up), _ptr(out), _dt(out), T, I, _stream()), "silu_mul")
+
+
+# -------------------------------------------------------------------- sampling
+def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out) -> None:
+    """out[r] = next token of row r from float32 logits [R, V].  Per-row device
+    arrays: temperature float32 (<= 0: greedy), top_k int32 (<= 0 off), top_p
+    float32 (>= 1 off), min_p float32 (0 off), uniform float32 in [0, 1).  All of
+    them None means every row is greedy.  scratch: float32 [R, V]."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 with unit inner stride")
+    if out.dtype != torch.int32 or out.numel() < R:
+        raise KernelError("sample: out must be int32 with one entry per row")
+    if temperature is not None:
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < R * V or not scratch.is_contiguous():
+            raise KernelError("sample: scratch must be contiguous float32 [rows, vocab]")
+        for t_, n_ in ((temperature, "temperature"), (top_p, "top_p"), (min_p, "min_p"), (uniform, "uniform")):
+            if t_ is None or t_.dtype != torch.float32 or t_.numel() < R:
+                raise KernelError(f"sample: {n_} must be float32 with one entry per row")
+        _i32(top_k, "top_k")
+    _check(library().arle_sample(_ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                 _ptr(min_p), _ptr(uniform), _ptr(scratch), _ptr(out), _stream()), "sample")

@@ -1,0 +1,50 @@
+"""Pre-norm block: x <- x + mixer(norm(x)); x <- x + ffn(norm(x))
+(infer/src/model/qwen3/prefill.rs:618-776).  The block never touches the residual
+itself: it hands branch outputs to the ``ResidualStream``, which folds each into
+the 32-bit residual inside the kernel of the next norm, the fusion cklxx/arle's
+decode path uses (infer/src/model/qwen3/batch_decode.rs:2422-2452)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import ClassVar
+
+from .base import Block
+from .registry import build_part, register_part
+
+
+@dataclass(frozen=True)
+class PreNormBlockSpec:
+    mixer_norm: object
+    mixer: object
+    ffn_norm: object
+    ffn: object
+    kind: ClassVar[str] = "prenorm_block"
+
+
+class PreNormBlock(Block):
+    def __init__(self, spec: PreNormBlockSpec):
+        self.spec = spec
+        self.mixer_norm = build_part(spec.mixer_norm)
+        self.mixer = build_part(spec.mixer)
+        self.ffn_norm = build_part(spec.ffn_norm)
+        self.ffn = build_part(spec.ffn)
+        self._parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+
+    def weight_decls(self):
+        return tuple(d for p in self._parts for d in p.weight_decls())
+
+    def load(self, tensors, dtype, device):
+        for p in self._parts:
+            p.load(tensors, dtype, device)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self._parts)
+
+    def forward(self, stream, ctx, cache, state):
+        h = stream.normed(self.mixer_norm, "normed_a")
+        stream.add(self.mixer.forward(h, ctx, cache, state))
+        h = stream.normed(self.ffn_norm, "normed_b")
+        stream.add(self.ffn.forward(h, ctx))
+
+
+register_part(PreNormBlockSpec.kind, PreNormBlock)

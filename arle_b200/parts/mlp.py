@@ -1,0 +1,61 @@
+"""Gated feed-forward (SwiGLU): down(act(gate(x)) * up(x)), no biases
+(infer/src/model/qwen3/prefill.rs:291-337).  Gate and up are packed row-wise into
+one [2I, H] matrix at load, the layout cklxx/arle offers as an option
+(infer/src/model/qwen3/weights.rs:98-122)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import ClassVar
+
+import torch
+
+from .. import ops
+from .base import FeedForward, WeightDecl
+from .registry import register_part
+
+
+@dataclass(frozen=True)
+class GatedMlpSpec:
+    prefix: str
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "silu"
+    kind: ClassVar[str] = "gated_mlp"
+
+
+class GatedMlp(FeedForward):
+    def __init__(self, spec: GatedMlpSpec):
+        if spec.activation != "silu":
+            raise ValueError(f"activation {spec.activation!r} not supported by the gated feed-forward (silu)")
+        self.spec = spec
+        self.w_gate_up = self.w_down = None
+
+    def weight_decls(self):
+        s, p = self.spec, self.spec.prefix
+        return (WeightDecl(p + "gate_proj.weight", (s.intermediate_size, s.hidden_size)),
+                WeightDecl(p + "up_proj.weight", (s.intermediate_size, s.hidden_size)),
+                WeightDecl(p + "down_proj.weight", (s.hidden_size, s.intermediate_size)))
+
+    def load(self, tensors, dtype, device):
+        p = self.spec.prefix
+        g, u, d = (tensors[p + n + "_proj.weight"] for n in ("gate", "up", "down"))
+        wt = dtype if dtype == torch.bfloat16 else (torch.float32 if torch.float32 in (g.dtype, u.dtype) else torch.bfloat16)
+        self.w_gate_up = torch.cat([g.to(device=device, dtype=wt), u.to(device=device, dtype=wt)], dim=0).contiguous()
+        self.w_down = d.to(device=device, dtype=dtype if dtype == torch.bfloat16 else d.dtype).contiguous()
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
+
+    def forward(self, x, ctx):
+        s = self.spec
+        T = x.shape[0]
+        gu = ctx.ws.get("gate_up", (T, 2 * s.intermediate_size), x.dtype)
+        ops.gemm(x, self.w_gate_up, gu)
+        act = ctx.ws.get("ffn_act", (T, s.intermediate_size), x.dtype)
+        ops.silu_mul(gu, act)
+        out = ctx.ws.get("ffn_out", (T, s.hidden_size), x.dtype)
+        ops.gemm(act, self.w_down, out)
+        return out
+
+
+register_part(GatedMlpSpec.kind, GatedMlp)

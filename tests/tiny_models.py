@@ -1,0 +1,33 @@
+"""Tiny Qwen3 configurations for the tests.  They differ in every size and option:
+layers, width, heads and groups (GQA 2, MQA 6, MHA), head size (16, 32, 48),
+feed-forward width, vocabulary (a power of two, an even and an odd non-power),
+rope base, norm eps, tied or untied output, and the key window (none; some layers)."""
+import os
+import tempfile
+
+from arle_b200.weights import write_random_model
+
+TINY_A = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=64, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, intermediate_size=128, vocab_size=256, rope_theta=10000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=512, hidden_act="silu",
+              bos_token_id=1, eos_token_id=2)
+TINY_B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_size=96, num_attention_heads=6,
+              num_key_value_heads=1, head_dim=32, intermediate_size=176, vocab_size=500, rope_theta=1000000.0,
+              rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=1024, hidden_act="silu",
+              bos_token_id=0, eos_token_id=3)
+TINY_C = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=4, hidden_size=72, num_attention_heads=3,
+              num_key_value_heads=3, head_dim=48, intermediate_size=100, vocab_size=301, rope_theta=500000.0,
+              rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=768, hidden_act="silu",
+              use_sliding_window=True, sliding_window=21, max_window_layers=2, bos_token_id=0, eos_token_id=5)
+INIT = {"A": dict(sigma=0.02, gain_jitter=0.1), "B": dict(sigma=0.03, gain_jitter=0.2),
+        "C": dict(sigma=0.05, gain_jitter=0.15)}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+PAGE_SIZES = {"A": 4, "B": 8, "C": 16}
+
+
+def make_model_dir(name: str, seed: int = 0, root: str = None, **init) -> str:
+    """Writes the tiny model into a fresh temporary folder and returns it."""
+    root = root or tempfile.mkdtemp(prefix=f"arle_tiny_{name}_")
+    kw = dict(INIT[name])
+    kw.update(init)
+    return write_random_model(os.path.join(root, name), CONFIGS[name], seed, **kw)
