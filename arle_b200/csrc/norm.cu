@@ -42,7 +42,7 @@ static int launch(float* resid, const void* delta, const int* rows, const float*
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {  // static shared memory counts against the 48 KB default too
     cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel<TA>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

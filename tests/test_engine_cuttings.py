@@ -1,0 +1,82 @@
+"""The engine against the plain model under every way of cutting the work: each
+request alone and whole; most of it in one step and the last 32 tokens one by one;
+portions of changing size down to two tokens; and mixed batches of up to four live
+requests on so few pages that they are used again.  Run on the GPU in float32 and
+bfloat16, and (the same scenarios, with the kernels replaced by their plain torch
+statements) on the CPU, where they test everything around the kernels."""
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import traces
+from arle_b200.engine import ModelRunner, load_model
+from tiny_models import CONFIGS, PAGE_SIZES, make_model_dir
+
+LENGTHS = {"A": [1, 5, 11, 23, 70, 130], "B": [2, 17, 40, 96, 67, 33], "C": [3, 50, 90, 120, 64, 35]}
+CUTS = ["whole", "tail_decode", "portions", "mixed"]
+# absolute tolerance on logits of magnitude ~1.5: float32 rounding through a few
+# layers; bfloat16 rounding of activations (8 mantissa bits) through the same.
+ATOL = {torch.float32: 2e-5, torch.bfloat16: 4e-2}
+MEAN = {torch.float32: 2e-6, torch.bfloat16: 6e-3}
+
+_cache = {}
+
+
+def model_and_oracle(name, tmp_path_factory):
+    if name not in _cache:
+        d = make_model_dir(name, seed=11, root=str(tmp_path_factory.mktemp(f"tiny{name}")))
+        cfg, w = plain.read_config(d), plain.read_weights(d)
+        reqs = traces.make_requests(cfg["vocab_size"], LENGTHS[name], seed=5)
+        oracle = {r: plain.forward(w, cfg, t) for r, t in reqs.items()}
+        _cache[name] = (d, reqs, oracle)
+    return _cache[name]
+
+
+def build_steps(cut, reqs):
+    if cut == "mixed":
+        return traces.mixed(reqs, seed=3)
+    return getattr(traces, cut)(reqs)
+
+
+def check(name, dtype, cut, device, tmp_path_factory):
+    d, reqs, oracle = model_and_oracle(name, tmp_path_factory)
+    steps = build_steps(cut, reqs)
+    ps = PAGE_SIZES[name]
+    pages = traces.peak_tokens(steps) // ps
+    model = load_model(d, dtype, device)
+    runner = ModelRunner(model, ps, pages, 4, device=device)
+    got = traces.run_trace(runner, steps)
+    runner.cache.check()
+    assert all(g.pool.num_free == g.pool.num_pages for g in runner.cache.groups), "pages not given back"
+    for r, want in oracle.items():
+        err = (got[r].double() - want).abs()
+        assert got[r].shape == want.shape
+        first_bad = (err.max(dim=1).values > ATOL[dtype]).nonzero()
+        assert err.max().item() <= ATOL[dtype], (
+            f"{name} {cut} {dtype}: request {r} first wrong position {int(first_bad[0])} of {len(reqs[r])}, "
+            f"max error {err.max().item():.3g}")
+        assert err.mean().item() <= MEAN[dtype]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cut", CUTS)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_cuttings_gpu(name, dtype, cut, tmp_path_factory):
+    check(name, dtype, cut, "cuda", tmp_path_factory)
+
+
+@pytest.mark.parametrize("cut", CUTS)
+@pytest.mark.parametrize("name,dtype", [("A", torch.float32), ("B", torch.bfloat16), ("C", torch.float32)],
+                         ids=["A-f32", "B-bf16", "C-f32"])
+def test_cuttings_around_the_kernels_cpu(name, dtype, cut, tmp_path_factory, cpu_kernels):
+    check(name, dtype, cut, "cpu", tmp_path_factory)
+
+
+def test_mixed_trace_reuses_pages():
+    reqs = traces.make_requests(100, LENGTHS["A"], seed=5)
+    steps = traces.mixed(reqs, seed=3)
+    assert traces.peak_tokens(steps) < sum(-(-len(t) // 64) * 64 for t in reqs.values())
+    assert max(len(s["entries"]) for s in steps) >= 3
+    assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"]) and \
+        any(len(e["tokens"]) == 2 for s in steps for e in s["entries"])

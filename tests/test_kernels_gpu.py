@@ -1,0 +1,275 @@
+"""Each CUDA kernel alone against its plain torch statement (tests/kernel_refs.py),
+in float32 and bfloat16, at sizes other than the engine's: widths that are no
+power of two, odd vocabularies, head sizes 16..256, several page sizes, groups
+of 1, 3 and 8 query heads per kv head."""
+import math
+
+import pytest
+import torch
+
+import kernel_refs as ref
+from arle_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H,T", [(300, 72, 5), (1000, 4096, 33), (17, 8, 1)])
+def test_embedding(dtype, V, H, T):
+    table = rnd(V, H, dtype=dtype)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32, device=DEV)
+    out = torch.empty(T, H, device=DEV)
+    exp = torch.empty(T, H, device=DEV)
+    ops.embedding(ids, table, out)
+    ref.embedding(ids, table, exp)
+    assert torch.equal(out, exp)
+
+
+def test_embedding_bad_id_sets_flag_and_writes_zeros():
+    table = rnd(10, 16)
+    ids = torch.tensor([3, 11, -1], dtype=torch.int32, device=DEV)
+    out = torch.full((3, 16), 7.0, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embedding(ids, table, out, err)
+    assert err.item() == 1 and torch.equal(out[0], table[3]) and out[1:].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,H", [(1, 64), (7, 260), (19, 4096), (3, 12288), (5, 100)])
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_rmsnorm(dtype, N, H, with_delta):
+    resid = rnd(N, H, scale=3.0, seed=1)
+    delta = rnd(N, H, dtype=dtype, seed=2) if with_delta else None
+    w = 1.0 + 0.2 * rnd(H, seed=3)
+    r1, r2 = resid.clone(), resid.clone()
+    out = torch.empty(N, H, dtype=dtype, device=DEV)
+    exp = torch.empty(N, H, dtype=dtype, device=DEV)
+    ops.rmsnorm(r1, delta, None, w, 1e-5, out, with_delta)
+    ref.rmsnorm(r2, delta, None, w, 1e-5, exp, with_delta)
+    torch.testing.assert_close(out.float(), exp.float(), **tol(dtype))
+    torch.testing.assert_close(r1, r2, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_rows_leave_residual(dtype):
+    N, H = 11, 200
+    resid, delta = rnd(N, H, seed=4), rnd(N, H, dtype=dtype, seed=5)
+    w = 1.0 + 0.1 * rnd(H, seed=6)
+    rows = torch.tensor([10, 0, 3], dtype=torch.int32, device=DEV)
+    before = resid.clone()
+    out = torch.empty(3, H, dtype=dtype, device=DEV)
+    exp = torch.empty(3, H, dtype=dtype, device=DEV)
+    ops.rmsnorm(resid, delta, rows, w, 1e-6, out, False)
+    ref.rmsnorm(before.clone(), delta, rows, w, 1e-6, exp, False)
+    torch.testing.assert_close(out.float(), exp.float(), **tol(dtype))
+    assert torch.equal(resid, before)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_residual_add(dtype):
+    resid, delta = rnd(9, 130, seed=1), rnd(9, 130, dtype=dtype, seed=2)
+    exp = resid + delta.float()
+    ops.residual_add(resid, delta)
+    assert torch.equal(resid, exp)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 100), (6, 176), (33, 12288)])
+def test_silu_mul(dtype, T, I):
+    gu = rnd(T, 2 * I, dtype=dtype, scale=2.0)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    exp = torch.empty(T, I, dtype=dtype, device=DEV)
+    ops.silu_mul(gu, out)
+    ref.silu_mul(gu, exp)
+    torch.testing.assert_close(out.float(), exp.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 301, 72), (70, 130, 100), (129, 65, 17), (3, 500, 96)])
+def test_gemm_f32_true_32bit(wdtype, M, N, K):
+    x = rnd(M, K, seed=1)
+    w = rnd(N, K, dtype=wdtype, seed=2)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm(x, w, out)
+    exp = (x.double() @ w.double().t())
+    # float32 products and sums: error of a K-term dot product, far below TF32's 1e-3
+    assert (out.double() - exp).abs().max().item() < 2e-6 * math.sqrt(K) * 4
+
+
+def test_gemm_f32_rows_do_not_depend_on_batch():
+    x, w = rnd(77, 200, seed=3), rnd(150, 200, seed=4)
+    full = torch.empty(77, 150, device=DEV)
+    ops.gemm(x, w, full)
+    for rows in ([0], [5, 6, 7], list(range(64, 77))):
+        part = torch.empty(len(rows), 150, device=DEV)
+        ops.gemm(x[rows].contiguous(), w, part)
+        assert torch.equal(part, full[rows])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (8, 4096, 1024), (130, 304, 72)])
+def test_gemm_bf16(M, N, K):
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+    exp = x.float() @ w.float().t()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm(x, w, out)
+    torch.testing.assert_close(out.float(), exp, rtol=2e-2, atol=2e-2 * math.sqrt(K) / 8)
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    ops.gemm(x, w, out32)
+    torch.testing.assert_close(out32, exp, rtol=1e-3, atol=1e-3)
+
+
+def _paged_setup(dtype, nq, nkv, hd, ps, lens, q_lens, seed=0):
+    """Random cache contents for requests of the given lengths, scattered pages."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lens)
+    pages_per = [-(-n // ps) for n in lens]
+    total_pages = sum(pages_per) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    width = max(pages_per)
+    bt = torch.full((R, width), -1, dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(pages_per):
+        bt[r, :n] = torch.tensor(perm[at:at + n], dtype=torch.int32)
+        at += n
+    kc = (torch.randn(total_pages, nkv, ps, hd, generator=g)).to(dtype).to(DEV)
+    vc = (torch.randn(total_pages, nkv, ps, hd, generator=g)).to(dtype).to(DEV)
+    positions, rows = [], []
+    for r, (n, ql) in enumerate(zip(lens, q_lens)):
+        positions += list(range(n - ql, n))
+        rows += [r] * ql
+    T = len(positions)
+    q = (torch.randn(T, nq * hd, generator=g)).to(dtype).to(DEV)
+    return (q, kc, vc, torch.tensor(positions, dtype=torch.int32, device=DEV),
+            torch.tensor(rows, dtype=torch.int32, device=DEV), bt.to(DEV))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,ps,window", [(4, 2, 16, 4, None), (6, 1, 32, 8, None), (3, 3, 48, 16, 21),
+                                                  (8, 1, 128, 16, None), (2, 2, 256, 32, 40), (5, 5, 80, 3, 7)])
+def test_paged_attention_plain(dtype, nq, nkv, hd, ps, window):
+    lens, q_lens = [1, 37, 150, 64], [1, 5, 1, 64]
+    q, kc, vc, pos, rows, bt = _paged_setup(dtype, nq, nkv, hd, ps, lens, q_lens)
+    out = torch.empty(q.shape[0], nq * hd, dtype=dtype, device=DEV)
+    exp = torch.empty_like(out).cpu()
+    ops.paged_attention(q, out, kc, vc, pos, rows, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window)
+    ref.paged_attention(q.cpu(), exp, kc.cpu(), vc.cpu(), pos.cpu(), rows.cpu(), bt.cpu(), nq, nkv, hd, ps,
+                        1 / math.sqrt(hd), window)
+    torch.testing.assert_close(out.float().cpu(), exp.float(), **tol(dtype))
+
+
+def test_paged_attention_finds_a_far_key():
+    """One key among hundreds, far back, is made to dominate: the output must be
+    that key's value row (a kernel that drops or misplaces a page would miss it)."""
+    nq, nkv, hd, ps = 4, 2, 64, 16
+    for far in (0, 15, 16, 333, 511):
+        q, kc, vc, pos, rows, bt = _paged_setup(torch.float32, nq, nkv, hd, ps, [600], [1], seed=far)
+        page, off = int(bt[0, far // ps]), far % ps
+        kc[page, :, off] = 0
+        kc[page, 0, off, :] = q[0, :hd] * 50           # kv head 0 serves q heads 0,1; align with q head 0
+        out = torch.empty(1, nq * hd, device=DEV)
+        ops.paged_attention(q, out, kc, vc, pos, rows, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), None)
+        torch.testing.assert_close(out[0, :hd], vc[page, 0, off], rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,ps,rot,norm", [(4, 2, 16, 4, 16, True), (6, 1, 32, 8, 32, True),
+                                                    (3, 3, 48, 16, 48, True), (8, 2, 128, 16, 128, True),
+                                                    (2, 1, 64, 16, 32, False), (2, 2, 256, 8, 0, True)])
+def test_attention_prep(dtype, nq, nkv, hd, ps, rot, norm):
+    T, pages = 23, 9
+    width = (nq + 2 * nkv) * hd
+    qkv = rnd(T, width, dtype=dtype, scale=2.0, seed=1)
+    pos = torch.randint(0, 5000, (T,), dtype=torch.int32, device=DEV)
+    slots = torch.randperm(pages * ps)[:T].to(torch.int32).to(DEV)
+    slots[3] = -1
+    qw = (1.0 + 0.2 * rnd(hd, seed=2)) if norm else None
+    kw = (1.0 + 0.2 * rnd(hd, seed=3)) if norm else None
+    inv = torch.pow(torch.tensor(1e4), -2.0 * torch.arange(rot // 2) / max(rot, 1)).float().to(DEV) if rot else None
+    kc = torch.zeros(pages, nkv, ps, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    a, b = qkv.clone(), qkv.clone()
+    kc2, vc2 = kc.clone(), vc.clone()
+    ops.attention_prep(a, pos, slots, qw, kw, 1e-6, inv, rot, kc, vc, nq, nkv, hd, ps)
+    ref.attention_prep(b, pos, slots, qw, kw, 1e-6, inv, rot, kc2, vc2, nq, nkv, hd, ps)
+    t = dict(rtol=3e-5, atol=3e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(a[:, :nq * hd].float(), b[:, :nq * hd].float(), **t)
+    torch.testing.assert_close(kc.float(), kc2.float(), **t)
+    assert torch.equal(vc, vc2)
+
+
+def test_attention_prep_q_only():
+    nq, hd, T = 4, 32, 6
+    q = rnd(T, nq * hd, seed=1)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    qw = 1.0 + 0.1 * rnd(hd, seed=2)
+    inv = torch.pow(torch.tensor(1e6), -2.0 * torch.arange(hd // 2) / hd).float().to(DEV)
+    a, b = q.clone(), q.clone()
+    ops.attention_prep(a, pos, None, qw, None, 1e-6, inv, hd, None, None, nq, 0, hd, 16)
+    ref.attention_prep(b, pos, None, qw, None, 1e-6, inv, hd, None, None, nq, 0, hd, 16)
+    torch.testing.assert_close(a, b, rtol=3e-5, atol=3e-5)
+
+
+@pytest.mark.parametrize("V", [256, 301, 151936])
+def test_sample_greedy_lowest_index_on_ties(V):
+    logits = rnd(5, V, seed=1)
+    logits[1, 7] = logits[1, V - 3] = 50.0
+    logits[2, :] = 0.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    ops.sample(logits, None, None, None, None, None, None, out)
+    exp = torch.empty(5, dtype=torch.int32)
+    ref.sample(logits.cpu(), None, None, None, None, None, None, exp)
+    assert out.cpu().tolist() == exp.tolist() and out[1].item() == 7 and out[2].item() == 0
+
+
+@pytest.mark.parametrize("V", [257, 5000])
+def test_sample_temperature_top_k_top_p(V):
+    R = 8
+    logits = rnd(R, V, scale=3.0, seed=2)
+    temp = torch.tensor([0.7, 1.0, 0.0, 1.3, 0.5, 1.0, 1.0, 0.9], device=DEV)
+    top_k = torch.tensor([-1, 5, -1, 1, 40, -1, 3, -1], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 1.0, 0.8, 0.5, 0.9, 1.0], device=DEV)
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.1], device=DEV)
+    for trial in range(6):
+        u = torch.rand(R, generator=torch.Generator().manual_seed(trial)).to(DEV)
+        scratch = torch.empty(R, V, device=DEV)
+        out = torch.empty(R, dtype=torch.int32, device=DEV)
+        ops.sample(logits, temp, top_k, top_p, min_p, u, scratch, out)
+        exp = torch.empty(R, dtype=torch.int32)
+        ref.sample(logits.cpu(), temp.cpu(), top_k.cpu(), top_p.cpu(), min_p.cpu(), u.cpu(), None, exp)
+        got = out.cpu().tolist()
+        for r in range(R):
+            if got[r] != exp[r].item():
+                # only a draw that falls within rounding of a CDF step may differ, by one kept token
+                p = torch.softmax(logits[r].double().cpu() / max(float(temp[r]), 1e-9), 0)
+                assert abs(got[r] - exp[r].item()) >= 1 and p[got[r]] > 0, (r, got[r], exp[r].item())
+                c = torch.cumsum(scratch[r].double().cpu(), 0)
+                assert abs(float(c[min(got[r], exp[r].item())]) - float(u[r]) * float(c[-1])) < 1e-5
+
+
+def test_sample_draws_follow_the_distribution():
+    V, n = 50, 4000
+    logits = rnd(1, V, scale=2.0, seed=5).repeat(n, 1)
+    u = torch.rand(n, generator=torch.Generator().manual_seed(1)).to(DEV)
+    ones = torch.ones(n, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(logits, ones, torch.full((n,), -1, dtype=torch.int32, device=DEV), ones, 0 * ones, u,
+               torch.empty(n, V, device=DEV), out)
+    freq = torch.bincount(out.long().cpu(), minlength=V).double() / n
+    p = torch.softmax(logits[0].double().cpu(), 0)
+    assert (freq - p).abs().max().item() < 0.03
+
+
+def test_refuses_cpu_tensors_loudly():
+    with pytest.raises(ops.KernelError):
+        ops.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
