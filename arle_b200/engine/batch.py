@@ -78,6 +78,7 @@ class StepContext:
         self.max_q_len = 0
         self.max_kv_len = 0
         self.decode_only = False
+        self.table_width = 0
         self.token_ids = self.positions = self.row_of_token = None
         self.q_indptr = self.kv_lens = self.state_slots = self.want_rows = None
         self.groups: List[GroupTables] = []
@@ -86,9 +87,11 @@ class StepContext:
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
 
     # ------------------------------------------------------------------ build
-    def build(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> "StepContext":
+    def build(self, entries: Sequence[StepEntry], starts: Sequence[int], table_width: Optional[int] = None) -> "StepContext":
         """``starts[i]`` is the number of tokens request i held before this step; the
-        cache manager has already made room for the new ones."""
+        cache manager has already made room for the new ones.  ``table_width`` fixes
+        the width of every block table (a captured graph needs the same layout at
+        every replay); by default each is as wide as the longest request needs."""
         cm = self.cache
         R = len(entries)
         q_lens = [len(e.tokens) for e in entries]
@@ -104,7 +107,11 @@ class StepContext:
         n_groups = len(cm.groups)
         widths = []
         for gi, g in enumerate(cm.groups):
-            widths.append(max(1, max(-(-kv // g.page_size) for kv in self.kv_lens_host)))
+            need = max(1, max(-(-kv // g.page_size) for kv in self.kv_lens_host))
+            if table_width is not None and need > table_width:
+                raise ValueError(f"a request needs {need} pages, the fixed table width is {table_width}")
+            widths.append(table_width if table_width is not None else need)
+        self.table_width = max(widths) if widths else 0
         # layout of the packed int32 array
         sizes = [T, T, T, R + 1, R, R, max(W, 1)]
         for gi in range(n_groups):

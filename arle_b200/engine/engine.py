@@ -1,0 +1,152 @@
+"""The Python entry point: ``Engine(model_path).generate(prompts, SamplingParams)``.
+
+It plays the role of cklxx/arle's ``LoadedInferenceEngine`` / ``complete()``
+(infer/src/server_engine/loaded.rs:48-99; request_handle_engine.rs:54-96) for
+token ids: load a model folder, size the cache, run the scheduler loop until the
+given requests are finished, return their tokens and finish reasons ("stop" or
+"length", infer/src/server_engine/types.rs:31-43).  Option names follow the
+reference's ``infer`` command line (infer/src/main.rs:27-237).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..sampling import Sampler, SamplingParams, request_rng
+from .batch import StepEntry
+from .loading import load_model, parse_dtype
+from .runner import ModelRunner
+from .scheduler import Scheduler, SchedulerConfig
+
+
+@dataclass
+class EngineOptions:
+    dtype: str = "bfloat16"
+    device: str = "cuda:0"
+    page_size: int = 16
+    num_pages: Optional[int] = None            # None: from free memory and mem_fraction_static
+    mem_fraction_static: float = 0.85
+    num_slots: int = 64                        # most requests running at a time
+    max_seq_len: Optional[int] = None          # most tokens a request may hold; None: max_position_embeddings
+    max_num_batched_tokens: int = 16384
+    chunked_prefill_size: int = 16384
+    max_prefill_tokens: Optional[int] = None
+    prefill_max_requests: Optional[int] = None
+    scheduler_mixed_policy: str = "mixed"
+    max_tokens: int = 256                      # default max_new_tokens of a request
+    seed: int = 42
+    cuda_graph: bool = True
+
+
+@dataclass
+class GenerationOutput:
+    request_id: object
+    prompt_token_ids: List[int]
+    token_ids: List[int]
+    finish_reason: str
+    preemptions: int = 0
+
+
+class Engine:
+    def __init__(self, model_path: Optional[str] = None, *, model=None, options: Optional[EngineOptions] = None, **kw):
+        self.options = options or EngineOptions(**kw)
+        o = self.options
+        dtype = parse_dtype(o.dtype)
+        if model is None:
+            if model_path is None:
+                raise ValueError("Engine needs a model folder (model_path) or a loaded model")
+            model = load_model(model_path, dtype, o.device)
+        elif model.dtype != dtype:
+            raise ValueError(f"the given model was loaded as {model.dtype}, the options ask for {dtype}")
+        self.model = model
+        max_seq = o.max_seq_len or model.spec.max_position
+        per_page = self._bytes_per_page(model, o.page_size, dtype)
+        pages = o.num_pages if o.num_pages is not None else self._pages_from_memory(per_page, o, max_seq)
+        self.runner = ModelRunner(model, o.page_size, pages, o.num_slots, max_seq, o.device)
+        if o.cuda_graph and hasattr(self.runner, "enable_graphs"):
+            self.runner.enable_graphs()
+        self.scheduler = Scheduler(self.runner.cache, SchedulerConfig(
+            o.max_num_batched_tokens, o.chunked_prefill_size, o.max_prefill_tokens, o.prefill_max_requests,
+            o.scheduler_mixed_policy), model.spec.stop_token_ids, o.max_tokens)
+        self.sampler = Sampler(model.spec.vocab_size, o.device)
+        self._rngs: Dict[object, object] = {}
+        self._next_id = 0
+
+    @staticmethod
+    def _bytes_per_page(model, page_size: int, dtype) -> int:
+        width = 2 if dtype == torch.bfloat16 else 4
+        return sum(2 * n.num_kv_heads * n.head_dim * page_size * width for n in model.cache_needs)
+
+    @staticmethod
+    def _pages_from_memory(per_page: int, o: EngineOptions, max_seq: int) -> int:
+        if per_page == 0:
+            return 1
+        cap = o.num_slots * -(-max_seq // o.page_size)
+        if torch.device(o.device).type != "cuda":
+            return min(cap, 4096)
+        free, total = torch.cuda.mem_get_info(torch.device(o.device))
+        budget = free - int((1.0 - o.mem_fraction_static) * total)
+        if budget < per_page * o.num_slots:
+            raise RuntimeError(f"not enough free device memory for the cache: {free >> 20} MiB free, "
+                               f"mem_fraction_static={o.mem_fraction_static}")
+        return max(1, min(cap, budget // per_page))
+
+    # ----------------------------------------------------------------- public
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, request_id=None):
+        rid = request_id if request_id is not None else f"req-{self._next_id}"
+        self._next_id += 1
+        vocab = self.model.spec.vocab_size
+        for t in prompt:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary [0, {vocab})")
+        req = self.scheduler.add_request(rid, prompt, params)
+        self._rngs[rid] = request_rng(self.options.seed, req.number, req.params)
+        return req
+
+    def step(self) -> list:
+        """One scheduler tick (one or two model steps).  Returns the requests that
+        finished in it."""
+        finished = []
+        for plan in self.scheduler.schedule():
+            entries = [StepEntry(e.request.rid, e.tokens, (e.count - 1,) if e.samples else ()) for e in plan.entries]
+            sampling = [e.request for e in plan.entries if e.samples]
+            logits = self.runner.step(entries)
+            sampled = []
+            if sampling:
+                sampled = self.sampler.sample(logits, [r.params for r in sampling], [self._rngs[r.rid] for r in sampling])
+            done = self.scheduler.on_step_done(plan, sampled)
+            for r in done:
+                self._rngs.pop(r.rid, None)
+            finished.extend(done)
+        return finished
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 on_token: Optional[Callable] = None) -> List[GenerationOutput]:
+        """Runs the given prompts (lists of token ids) to completion and returns one
+        ``GenerationOutput`` per prompt, in order."""
+        if isinstance(sampling_params, SamplingParams) or sampling_params is None:
+            sampling_params = [sampling_params] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+        seen = {r.rid: 0 for r in reqs}
+        while any(r.finish_reason is None for r in reqs):
+            if not self.scheduler.has_work():
+                raise RuntimeError("scheduler has no work but requests are unfinished")
+            self.step()
+            if on_token is not None:
+                for r in reqs:
+                    for t in r.output[seen[r.rid]:]:
+                        on_token(r.rid, t)
+                    seen[r.rid] = len(r.output)
+        self.scheduler.finished.clear()
+        return [GenerationOutput(r.rid, r.prompt, list(r.output), r.finish_reason, r.preemptions) for r in reqs]
+
+    def stats(self) -> dict:
+        s = dict(self.scheduler.stats)
+        s.update(model_steps=self.runner.steps_run, tokens_run=self.runner.tokens_run,
+                 free_pages=self.runner.cache.free_pages(), total_pages=self.runner.cache.total_pages())
+        return s

@@ -33,6 +33,39 @@ class ModelRunner:
         self.ctx = StepContext(self.cache, self.ws)
         self.steps_run = 0
         self.tokens_run = 0
+        self.graph_steps = 0
+        self._graphs = None            # None: graphs off; else {(rows, table width): _DecodeGraph}
+        self._max_graph_rows = 0
+
+    # ----------------------------------------------------------------- graphs
+    def enable_graphs(self, max_rows: int = 256) -> None:
+        """Decode-only steps (every entry one token whose logits are wanted) of up to
+        ``max_rows`` rows run as CUDA graphs, one per (row count, block-table width
+        rounded up to a power of two), captured at first use.  cklxx/arle captures
+        one graph per batch size the same way
+        (infer/src/model/qwen3/batch_decode.rs:1695-1730)."""
+        if self.device.type != "cuda":
+            raise RuntimeError("CUDA graphs need a CUDA device")
+        self._graphs = {}
+        self._max_graph_rows = max_rows
+
+    def disable_graphs(self) -> None:
+        self._graphs = None
+
+    def _graph_key(self, entries, starts):
+        if self._graphs is None or len(entries) > self._max_graph_rows:
+            return None
+        if any(len(e.tokens) != 1 or tuple(e.want) != (0,) for e in entries):
+            return None
+        pages = max(-(-(s + 1) // self.cache.page_size) for s in starts)
+        width = 1 << max(3, (pages - 1).bit_length())
+        return (len(entries), width)
+
+    def _run_graph(self, key, entries, starts):
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = _DecodeGraph(self, key[1])
+        return g.run(entries, starts)
 
     # --------------------------------------------------------------- requests
     def add_request(self, rid) -> None:
@@ -59,8 +92,13 @@ class ModelRunner:
         starts = [self.cache.num_tokens(e.request) for e in entries]
         self.cache.append([(e.request, len(e.tokens)) for e in entries])
         try:
-            ctx = self.ctx.build(entries, starts)
-            logits = self.model.forward(ctx)
+            key = self._graph_key(entries, starts)
+            if key is not None:
+                ctx, logits = self._run_graph(key, entries, starts)
+                self.graph_steps += 1
+            else:
+                ctx = self.ctx.build(entries, starts)
+                logits = self.model.forward(ctx)
         except Exception:
             for e, s in zip(entries, starts):
                 self.cache.truncate(e.request, s)
@@ -70,3 +108,37 @@ class ModelRunner:
         self.steps_run += 1
         self.tokens_run += ctx.num_tokens
         return logits
+
+
+class _DecodeGraph:
+    """A captured decode step for one (row count, block-table width).  It owns its
+    step tables and its workspace, so their addresses never change; a replay
+    copies the step's tables into place and launches the graph."""
+
+    def __init__(self, runner: ModelRunner, table_width: int):
+        self.runner = runner
+        self.table_width = table_width
+        self.ws = Workspace(runner.device)
+        self.ctx = StepContext(runner.cache, self.ws)
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+
+    def run(self, entries, starts):
+        from .. import ops
+
+        ctx = self.ctx.build(entries, starts, self.table_width)
+        if self.graph is None:
+            model = self.runner.model
+            model.forward(ctx)                      # eager once: allocates every workspace buffer
+            torch.cuda.synchronize(self.runner.device)
+            self.ws.frozen = True
+            before = ops.launch_count()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.logits = model.forward(ctx)
+            self.launches = ops.launch_count() - before
+            self.graph = graph
+        self.graph.replay()
+        ops.add_launches(self.launches)
+        return ctx, self.logits

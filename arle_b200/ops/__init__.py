@@ -21,6 +21,18 @@ import torch
 from . import build as _build
 
 _LIB = None
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (graph replays count what they hold)."""
+    return _LAUNCHES
+
+
+def add_launches(n: int) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
 
 _P, _I, _F = c_void_p, c_int, c_float
 _SIGNATURES = {
@@ -74,7 +86,9 @@ def _stream():
 
 
 def _check(code: int, what: str):
+    global _LAUNCHES
     if code == 0:
+        _LAUNCHES += 1
         return
     if code == -2:
         raise KernelError(f"{what}: sizes not supported by this kernel")

@@ -1,0 +1,265 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-8B layer sizes, one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with every
+request at a 2,048-token context (device time of K decode steps, CUDA events);
+``points`` holds batch 1 and 64; ``prefill`` one 2,048-token prompt; ``roofline``
+the bytes the decode step must read (each weight once + the live requests' cache)
+over its time against the measured copy bandwidth; ``e2e`` the same decode metric
+through ``Engine.generate`` with token ids going in from and coming back to the
+host.  Weights are seeded random, token ids uniform random, the cache of the
+device-timed runs is filled with random values (synthetic data).  The engine is a
+single-GPU one: for --gpus above 1 it says so and exits with 2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
+                num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1e6,
+                rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu")
+CONTEXT = 2048
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            with open(p) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d.get("bf16_tflops", 1590.0)),
+                    "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a region is timed."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.lines = None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                mhz.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than Qwen3-8B's 36 (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cuda-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "cklxx/arle's engine is a Rust workspace (no cargo/rustc in this image); the one offline pip "
+                          "install of the reference yields only its tooling metadata (arle-pytools), no engine"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    from arle_b200 import ops
+    from arle_b200.engine import ModelRunner, StepEntry, random_model
+    from arle_b200.engine.engine import Engine, EngineOptions
+    from arle_b200.sampling import Sampler, SamplingParams
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    layers = args.layers or QWEN3_8B["num_hidden_layers"]
+    model = random_model(QWEN3_8B, seed=0, dtype="bfloat16", device=dev, num_layers=layers)
+    spec = model.spec
+    vocab = spec.vocab_size
+    page = 16
+    max_batch = max(64, args.batch)
+    per_req = CONTEXT + args.steps + args.warmup + 64
+    pages = max_batch * -(-per_req // page) + 64
+    runner = ModelRunner(model, page, pages, max_batch, CONTEXT * 2 + 1024, dev)
+    if not args.no_cuda_graph:
+        runner.enable_graphs()
+    for g in runner.cache.groups:
+        g.kv.normal_(0.0, 0.5)                                   # synthetic cache contents
+    sampler = Sampler(vocab, dev)
+    gen = torch.Generator().manual_seed(1)
+    weight_bytes = model.weight_bytes_per_step()
+    kv_bytes_per_token = runner.cache.bytes_per_token()
+
+    def decode_run(batch, steps, warmup, clocks=None):
+        rids = [f"b{batch}-{i}" for i in range(batch)]
+        for r in rids:
+            runner.add_request(r)
+        runner.cache.append([(r, CONTEXT - 1) for r in rids])      # contexts of 2,047 tokens; the first step makes 2,048
+        toks = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+        greedy = [SamplingParams()] * batch
+
+        def one():
+            nonlocal toks
+            logits = runner.step([StepEntry(r, [t], (0,)) for r, t in zip(rids, toks)])
+            toks = sampler.sample(logits, greedy, [None] * batch)
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        if clocks:
+            clocks.start()
+        l0 = ops.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        launches = ops.launch_count() - l0
+        ctx_mid = CONTEXT + warmup + steps // 2
+        for r in rids:
+            runner.end_request(r)
+        return ms, launches, ctx_mid
+
+    clocks = ClockSampler()
+    ms, launches, ctx_mid = decode_run(args.batch, args.steps, args.warmup, clocks)
+    clk = clocks.stop()
+    value = args.batch * 1000.0 / ms
+    step_bytes = weight_bytes + args.batch * ctx_mid * kv_bytes_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    points = {}
+    for b in (1, 64):
+        m, _, _ = decode_run(b, max(8, args.steps // 2), args.warmup)
+        points[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
+
+    # prefill of one 2,048-token prompt, one step
+    def prefill_once(tag):
+        rid = f"p-{tag}"
+        ids = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        runner.step([StepEntry(rid, ids, (PREFILL_TOKENS - 1,))])
+        e1.record()
+        torch.cuda.synchronize()
+        runner.end_request(rid)
+        return e0.elapsed_time(e1)
+
+    for i in range(3):
+        prefill_once(f"w{i}")
+    pf_ms = sorted(prefill_once(f"t{i}") for i in range(5))[2]
+    c = model.config
+    mm_params = layers * (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
+                          + c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+    T = PREFILL_TOKENS
+    flops = 2.0 * T * mm_params + 2.0 * vocab * c.hidden_size \
+        + layers * 4.0 * c.num_attention_heads * c.head_dim * (T * (T + 1) / 2)
+    pf_tflops = flops / (pf_ms * 1e-3) / 1e12
+    prefill = {"value": round(T * 1000.0 / pf_ms, 1), "tokens": T, "ms": round(pf_ms, 3),
+               "frac": round(pf_tflops / pk["bf16_tflops"], 4), "tflops": round(pf_tflops, 1)}
+
+    # end to end through the public entry point: host token ids in, host token ids out
+    e2e = None
+    if not args.no_e2e:
+        del runner
+        torch.cuda.empty_cache()
+        n_new = args.steps + 1
+        eng = Engine(model=model, options=EngineOptions(
+            dtype="bfloat16", device="cuda:0", page_size=page, num_pages=args.batch * -(-(CONTEXT + n_new + 16) // page) + 8,
+            num_slots=args.batch, max_seq_len=CONTEXT * 2 + 1024, chunked_prefill_size=CONTEXT,
+            max_prefill_tokens=args.batch * CONTEXT, max_num_batched_tokens=args.batch * CONTEXT + 64,
+            cuda_graph=not args.no_cuda_graph))
+        prompts = [torch.randint(0, vocab, (CONTEXT,), generator=gen).tolist() for _ in range(args.batch)]
+        stamps = []
+
+        def on_token(rid, tok):
+            stamps.append(time.perf_counter())
+
+        eng.generate(prompts, SamplingParams(max_new_tokens=n_new, ignore_eos=True), on_token=on_token)
+        torch.cuda.synchronize()
+        # all prompts are prefilled in the first tick, which yields each request's first token;
+        # the decode steps after it are what is timed
+        first_done = stamps[args.batch - 1]
+        decoded = len(stamps) - args.batch
+        dt = stamps[-1] - first_done
+        meta_bytes = 4 * (3 * args.batch + (args.batch + 1) + 3 * args.batch
+                          + args.batch * eng.runner.ctx.table_width + args.batch)
+        e2e = {"value": round(decoded / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(meta_bytes),
+               "d2h_bytes_per_step": 4 * args.batch, "decoded_tokens": decoded}
+
+    out = {
+        "metric": "decode tokens/s at batch 8, 2048-token context (Qwen3-8B sizes, bf16, one B200)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded random weights, uniform random token ids, random cache contents)",
+        "impl": "ours",
+        "config": {"model": "Qwen3-8B sizes, random weights", "layers": layers, "layers_of_config": 36,
+                   "hidden_size": c.hidden_size, "num_attention_heads": c.num_attention_heads,
+                   "num_key_value_heads": c.num_key_value_heads, "head_dim": c.head_dim,
+                   "intermediate_size": c.intermediate_size, "vocab_size": vocab, "global_batch": args.batch,
+                   "seq_len": CONTEXT, "page_size": page, "parallelism": "single-gpu",
+                   "cuda_graph": not args.no_cuda_graph, "l2": "inputs larger than L2 (weights read once per step)",
+                   "peaks": pk["source"]},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"], "bytes_per_step": int(step_bytes)},
+        "points": points,
+        "e2e": e2e,
+        "gpu_launches": int(launches),
+        "clocks": clk,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,148 @@
+"""Generation through the Python entry point and the command line on the GPU:
+greedy output equals the plain model's; temperature sampling is seeded, does not
+depend on the batch, and follows the plain sampler; page pressure preempts without
+changing the output; decode steps run as CUDA graphs."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from arle_b200 import Engine, SamplingParams
+from tiny_models import PAGE_SIZES, make_model_dir
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PROMPTS = {"A": [1, 5, 11, 23], "B": [2, 17, 40], "C": [3, 30, 55]}
+STEPS = {"A": 12, "B": 20, "C": 16}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name in "ABC":
+        d = make_model_dir(name, seed=21, root=str(tmp_path_factory.mktemp(f"gen{name}")))
+        cfg, w = plain.read_config(d), plain.read_weights(d)
+        g = torch.Generator().manual_seed(2)
+        prompts = [torch.randint(6, cfg["vocab_size"], (n,), generator=g).tolist() for n in PROMPTS[name]]
+        out[name] = (d, cfg, w, prompts)
+    return out
+
+
+@pytest.mark.parametrize("graph", [True, False], ids=["graph", "eager"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_equals_plain_model_f32(models, name, graph):
+    d, cfg, w, prompts = models[name]
+    eng = Engine(d, dtype="float32", page_size=PAGE_SIZES[name], num_pages=64, num_slots=4, chunked_prefill_size=7,
+                 max_num_batched_tokens=24, cuda_graph=graph)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=STEPS[name], ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain.generate_greedy(w, cfg, p, STEPS[name]) and o.finish_reason == "length"
+    assert (eng.runner.graph_steps > 0) == graph
+    eng.runner.cache.check()
+    assert eng.runner.cache.free_pages() == eng.runner.cache.total_pages()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_bf16_stays_on_the_plain_models_best(models, name):
+    d, cfg, w, prompts = models[name]
+    eng = Engine(d, dtype="bfloat16", page_size=PAGE_SIZES[name], num_pages=64, num_slots=4)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=STEPS[name], ignore_eos=True))
+    same = 0
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        for t in o.token_ids:
+            lg = plain.forward(w, cfg, toks)[-1]
+            assert lg[t] >= lg.max() - 0.05          # a bfloat16 flip is only possible between near-ties
+            same += int(t == int(lg.argmax()))
+            toks.append(t)
+    assert same >= 0.9 * sum(len(o.token_ids) for o in outs)
+
+
+def test_temperature_sampling_seeded_and_batch_independent(models):
+    d, cfg, w, prompts = models["B"]
+    sp = [SamplingParams(temperature=0.7, seed=100 + i, max_new_tokens=20, ignore_eos=True) for i in range(3)]
+    kw = dict(dtype="float32", page_size=8, num_pages=64, num_slots=4)
+    together = Engine(d, **kw).generate(prompts, sp)
+    again = Engine(d, **kw).generate(prompts, sp)
+    alone = [Engine(d, **kw).generate([p], [s])[0] for p, s in zip(prompts, sp)]
+    assert [o.token_ids for o in together] == [o.token_ids for o in again] == [o.token_ids for o in alone]
+    assert len({tuple(o.token_ids) for o in together}) == 3
+    # each token is what the plain sampler draws from the plain model's logits with the same uniform number
+    import random
+    for p, s, o in zip(prompts, sp, together):
+        rng, toks = random.Random(s.seed), list(p)
+        for t in o.token_ids:
+            u = rng.random()
+            pr = plain.sampling_distribution(plain.forward(w, cfg, toks)[-1], 0.7)
+            want = plain.sample_from(pr, u)
+            if t != want:                               # only when u falls within rounding of a CDF step
+                c = torch.cumsum(pr, 0)
+                assert abs(float(c[min(t, want)]) - u) < 1e-4
+            toks.append(t)
+
+
+def test_top_k_top_p_only_emit_allowed_tokens(models):
+    d, cfg, w, prompts = models["A"]
+    eng = Engine(d, dtype="float32", page_size=4, num_pages=64, num_slots=4)
+    sp = SamplingParams(temperature=1.5, top_k=5, top_p=0.9, seed=3, max_new_tokens=12, ignore_eos=True)
+    for p, o in zip(prompts, eng.generate(prompts, sp)):
+        toks = list(p)
+        for t in o.token_ids:
+            pr = plain.sampling_distribution(plain.forward(w, cfg, toks)[-1], 1.5, top_k=5, top_p=0.9)
+            assert pr[t] > 0
+            toks.append(t)
+
+
+def test_stop_token_ends_with_stop_and_is_not_emitted(models):
+    d, cfg, w, prompts = models["A"]
+    ref = plain.generate_greedy(w, cfg, prompts[2], 12)
+    stop = ref[4]
+    first = ref.index(stop)
+    eng = Engine(d, dtype="float32", page_size=4, num_pages=64, num_slots=4)
+    o = eng.generate([prompts[2]], SamplingParams(max_new_tokens=12, stop_token_ids=(stop,)))[0]
+    assert o.finish_reason == "stop" and o.token_ids == ref[:first]
+
+
+def test_page_pressure_preempts_and_output_is_unchanged(models):
+    d, cfg, w, prompts = models["A"]
+    eng = Engine(d, dtype="float32", page_size=4, num_pages=14, num_slots=4, chunked_prefill_size=16)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=12, ignore_eos=True))
+    assert sum(o.preemptions for o in outs) > 0
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain.generate_greedy(w, cfg, p, 12)
+    eng.runner.cache.check()
+
+
+def test_split_policy_gives_the_same_tokens(models):
+    d, cfg, w, prompts = models["B"]
+    kw = dict(dtype="float32", page_size=8, num_pages=64, num_slots=4, chunked_prefill_size=5, max_num_batched_tokens=12)
+    a = Engine(d, scheduler_mixed_policy="mixed", **kw).generate(prompts, SamplingParams(max_new_tokens=10, ignore_eos=True))
+    b = Engine(d, scheduler_mixed_policy="split", **kw).generate(prompts, SamplingParams(max_new_tokens=10, ignore_eos=True))
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+
+
+def test_long_decoding(models):
+    d, cfg, w, prompts = models["C"]
+    eng = Engine(d, dtype="float32", page_size=16, num_pages=40, num_slots=2)
+    o = eng.generate([prompts[0]], SamplingParams(max_new_tokens=300, ignore_eos=True))[0]
+    toks = list(prompts[0]) + o.token_ids
+    lg = plain.forward(w, cfg, toks[:-1])
+    for i in range(len(prompts[0]) - 1, len(toks) - 1):      # teacher-forced: every emitted token is the plain argmax
+        assert lg[i].max() - lg[i][toks[i + 1]] < 1e-4
+    assert len(o.token_ids) == 300
+
+
+def test_command_line_run_json(models):
+    d, cfg, w, prompts = models["A"]
+    r = subprocess.run([sys.executable, "-m", "arle_b200", "--model-path", d, "--max-tokens", "6", "--dtype", "float32",
+                        "--page-size", "4", "--num-pages", "64", "--num-slots", "4", "--ignore-eos", "run", "--prompt",
+                        " ".join(map(str, prompts[1])), "--prompt", ",".join(map(str, prompts[3])), "--json"],
+                       cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    doc = json.loads(r.stdout.strip().splitlines()[-1])
+    assert [o["token_ids"] for o in doc["outputs"]] == [plain.generate_greedy(w, cfg, prompts[i], 6) for i in (1, 3)]
+    assert doc["outputs"][0]["finish_reason"] == "length" and doc["outputs"][0]["usage"]["completion_tokens"] == 6
