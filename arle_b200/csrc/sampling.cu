@@ -188,3 +188,67 @@ ARLE_API int arle_sample(const float* logits, int ld, int rows, int vocab, const
                                                 scratch, out);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// arle_sample_static: the same sampling kernel for callers that cannot allocate
+// device memory.  See no_alloc.h for the contract.  The probabilities go into a
+// fixed array that is part of this library's device image instead of a buffer
+// from the caller.
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_sample_scratch[ARLE_SAMPLE_STATIC_MAX_FLOATS];
+
+// In host code g_sample_scratch names a host-side shadow of the device array, not
+// a device address, so the address the kernel gets is asked from the runtime:
+// once per device, with that device current, and kept here.
+constexpr int kMaxDevices = 64;
+static float* g_scratch_addr[kMaxDevices];
+
+static int scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return ARLE_E_BADARG;
+  float* p = __atomic_load_n(&g_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void* sym = nullptr;
+    e = cudaGetSymbolAddress(&sym, g_sample_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (!sym) return ARLE_E_BADARG;
+    p = (float*)sym;
+    __atomic_store_n(&g_scratch_addr[dev], p, __ATOMIC_RELEASE);   // every thread would store the same value
+  }
+  *out = p;
+  return 0;
+}
+
+ARLE_API long long arle_sample_static_max_floats(void) { return (long long)ARLE_SAMPLE_STATIC_MAX_FLOATS; }
+
+ARLE_API const char* arle_no_alloc_error_string(int code) {
+  switch (code) {
+    case 0: return "success";
+    case ARLE_E_TOO_LARGE: return "arle_sample_static: rows * vocab exceeds ARLE_SAMPLE_STATIC_MAX_FLOATS, the size of the built-in scratch array";
+    case ARLE_E_BADARG: return "arle_sample_static: bad argument (null pointer, vocab <= 0, ld < vocab, or device ordinal out of range)";
+    case ARLE_E_UNSUPPORTED: return "arle_sample_static: sizes not supported";
+    default: return code > 0 ? "arle_sample_static: CUDA runtime error (the code is a cudaError_t)" : "arle_sample_static: unknown error";
+  }
+}
+
+ARLE_API int arle_sample_static(const float* logits, int ld, int rows, int vocab, const float* temperature,
+                                const int* top_k, const float* top_p, const float* min_p, const float* uniform,
+                                int* out, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (!logits || !out || vocab <= 0 || ld < vocab) return ARLE_E_BADARG;
+  if (temperature && !uniform) return ARLE_E_BADARG;
+  if ((long long)rows * (long long)vocab > (long long)ARLE_SAMPLE_STATIC_MAX_FLOATS) return ARLE_E_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  // Nothing in the scratch has to start at zero: the kernel writes every
+  // probability of a row before it reads any, so the last call's leftovers are
+  // overwritten, not cleared.
+  sample_kernel<<<rows, kSampleThreads, 0, s>>>(logits, ld, vocab, temperature, top_k, top_p, min_p, uniform,
+                                                scratch, out);
+  return launch_status();
+}
