@@ -78,6 +78,7 @@ class StepContext:
         self.max_q_len = 0
         self.max_kv_len = 0
         self.decode_only = False
+        self.num_single = 0
         self.table_width = 0
         self.token_ids = self.positions = self.row_of_token = None
         self.q_indptr = self.kv_lens = self.state_slots = self.want_rows = None
@@ -104,6 +105,7 @@ class StepContext:
         self.max_q_len = max(q_lens)
         self.max_kv_len = max(self.kv_lens_host)
         self.decode_only = self.max_q_len == 1
+        self.num_single = sum(1 for n in q_lens if n == 1)
         n_groups = len(cm.groups)
         widths = []
         for gi, g in enumerate(cm.groups):

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "arle_silu_mul": [_P, _P, _I, _I, _I, _P],
     "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
 }
@@ -223,10 +225,70 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
     _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _i32(block_table, "block_table")
     if block_table.stride(1) != 1:
         raise KernelError("paged_attention: block table rows must be contiguous")
+    if batch is not None and fast_attention_supported(q, nq, nkv, hd):
+        if batch.max_q_len > 1:
+            paged_attention_prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd,
+                                    page_size, scale, window, batch.max_q_len, skip_single=batch.num_single > 0)
+        if batch.num_single > 0:
+            splits = decode_splits(batch.num_rows, nkv, block_table.shape[1] * page_size)
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = batch.ws.get("attn_part_o", (batch.num_rows * nq * splits * hd,), torch.float32)
+                part_ml = batch.ws.get("attn_part_ml", (batch.num_rows * nq * splits * 2,), torch.float32)
+            paged_attention_decode(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd,
+                                   page_size, scale, window, splits, part_o, part_ml)
+        return
     _check(library().arle_paged_attention_plain(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), _ptr(positions), _ptr(row_of_token),
         _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
         int(window) if window else 0, T, _stream()), "paged_attention")
+
+
+def fast_attention_supported(q, nq: int, nkv: int, hd: int) -> bool:
+    """The tensor-core attention kernels take bfloat16, head sizes 64 and 128, up to
+    16 query heads per kv head and 16-byte aligned query rows; everything else
+    runs on the general kernel."""
+    return (q.dtype == torch.bfloat16 and hd in (64, 128) and nq // nkv <= 16 and q.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0)
+
+
+def decode_splits(rows: int, nkv: int, kv_bound: int) -> int:
+    """Splits along the keys so that about three CTAs per SM are in flight, never
+    more than one per 64-key tile of the longest request the tables allow."""
+    target = 148 * 3
+    splits = -(-target // max(1, rows * nkv))
+    return max(1, min(splits, -(-kv_bound // 64), 64))
+
+
+def paged_attention_decode(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
+                           window, splits: int, part_o=None, part_ml=None) -> None:
+    """Split-KV attention of the rows that have exactly one query (others are
+    skipped).  q_indptr int32 [R+1], kv_lens int32 [R] (keys after this step).
+    part_o / part_ml: float32 scratch of R*nq*splits*hd and R*nq*splits*2 elements
+    when splits > 1."""
+    R = kv_lens.numel()
+    if splits > 1 and (part_o is None or part_ml is None or part_o.numel() < R * nq * splits * hd
+                       or part_ml.numel() < R * nq * splits * 2 or part_o.dtype != torch.float32):
+        raise KernelError("paged_attention_decode: scratch for the splits is missing or too small")
+    _i32(q_indptr, "q_indptr"), _i32(kv_lens, "kv_lens"), _i32(block_table, "block_table")
+    _check(library().arle_paged_attention_decode(
+        _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_indptr), _ptr(kv_lens),
+        _ptr(block_table), block_table.stride(0), _ptr(part_o), _ptr(part_ml), nq, nkv, hd, page_size, float(scale),
+        int(window) if window else 0, R, int(splits), _stream()), "paged_attention_decode")
+    if splits > 1:
+        add_launches(1)
+
+
+def paged_attention_prefill(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
+                            window, max_q_len: int, skip_single: bool = False) -> None:
+    """Flash-attention over the paged cache for rows with several queries (and,
+    unless skip_single, for single-query rows too)."""
+    R = kv_lens.numel()
+    _i32(q_indptr, "q_indptr"), _i32(kv_lens, "kv_lens"), _i32(block_table, "block_table")
+    _check(library().arle_paged_attention_prefill(
+        _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_indptr), _ptr(kv_lens),
+        _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
+        int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _stream()), "paged_attention_prefill")
 
 
 # ------------------------------------------------------------------ activation

@@ -273,3 +273,83 @@ def test_sample_draws_follow_the_distribution():
 def test_refuses_cpu_tensors_loudly():
     with pytest.raises(ops.KernelError):
         ops.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
+
+
+# ----------------------------------------------------- tensor-core attention kernels
+def _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=0, scale_q=1.0):
+    q, kc, vc, pos, rows, bt = _paged_setup(torch.bfloat16, nq, nkv, hd, ps, lens, q_lens, seed)
+    q = (q.float() * scale_q).to(torch.bfloat16)
+    qi = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    return q, kc, vc, pos, rows, bt, qi, kv
+
+
+def _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, window):
+    exp = torch.empty(q.shape[0], nq * hd, dtype=torch.bfloat16)
+    ref.paged_attention(q.cpu(), exp, kc.cpu(), vc.cpu(), pos.cpu(), rows.cpu(), bt.cpu(), nq, nkv, hd, ps,
+                        1 / math.sqrt(hd), window)
+    return exp.float()
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("nq,nkv,hd,ps,window", [(32, 8, 128, 16, None), (6, 1, 64, 8, None), (16, 1, 128, 32, None),
+                                                  (4, 4, 128, 16, 100), (8, 2, 64, 4, 33), (3, 1, 128, 5, None)])
+def test_decode_attention_kernel(nq, nkv, hd, ps, window, splits):
+    lens = [1, 63, 64, 65, 700, 2049, 17]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, [1] * len(lens), seed=3)
+    R = len(lens)
+    out = torch.zeros(R, nq * hd, dtype=torch.bfloat16, device=DEV)
+    po = torch.full((R * nq * splits * hd,), float("nan"), device=DEV)       # stale scratch must not leak
+    pml = torch.full((R * nq * splits * 2,), float("nan"), device=DEV)
+    ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, splits, po, pml)
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, window)
+    torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,ps,window", [(32, 8, 128, 16, None), (6, 1, 64, 8, None), (4, 4, 128, 16, 70),
+                                                  (8, 2, 64, 4, 33), (3, 1, 128, 5, 64), (2, 1, 128, 64, 65)])
+def test_prefill_attention_kernel(nq, nkv, hd, ps, window):
+    lens, q_lens = [130, 300, 64, 65, 9, 200], [130, 2, 64, 3, 1, 77]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=4)
+    out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_prefill(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, max(q_lens))
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, window)
+    torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+
+
+def test_prefill_and_decode_kernels_split_a_mixed_step():
+    nq, nkv, hd, ps = 8, 2, 128, 16
+    lens, q_lens = [100, 40, 7, 300], [1, 40, 1, 11]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=5)
+    out = torch.full((q.shape[0], nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_prefill(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), None, 40, skip_single=True)
+    assert out[0].isnan().all() and out[41].isnan().all() and not out[1:41].isnan().any()
+    ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), None, 1)
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, None)
+    torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+def test_fast_attention_sees_one_far_key_and_the_windows_edge(kernel):
+    """Peaked attention: the query is aligned with exactly one key far back, so the
+    output must be that key's value; with a window that ends one key short of it,
+    the key must be invisible."""
+    nq, nkv, hd, ps = 4, 1, 128, 16
+    n = 1000
+    for far in (0, 63, 64, 500, 998):
+        lens, q_lens = ([n], [1]) if kernel == "decode" else ([n], [3])
+        q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=far)
+        page, off = int(bt[0, far // ps]), far % ps
+        unit = torch.zeros(hd)
+        unit[far % hd] = 1.0
+        kc[page, 0, off] = (unit * 40).to(torch.bfloat16).to(DEV)
+        q[-1, :hd] = (unit * 40).to(torch.bfloat16).to(DEV)           # last query, head 0
+        for window, visible in ((None, True), (n - far, True), (n - far - 1, False)):
+            out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
+            if kernel == "decode":
+                ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, 4,
+                                           torch.empty(nq * 4 * hd, device=DEV), torch.empty(nq * 8, device=DEV))
+            else:
+                ops.paged_attention_prefill(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, 3)
+            close = (out[-1, :hd].float() - vc[page, 0, off].float()).abs().max().item() < 2e-2
+            assert close == visible, (far, window)

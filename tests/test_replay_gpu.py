@@ -17,7 +17,7 @@ from tiny_models import make_model_dir
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-LENGTHS = {"B": [40, 96, 67, 33, 120, 51], "C": [50, 90, 140, 64, 35]}
+LENGTHS = {"B": [40, 96, 67, 33, 120, 51], "C": [50, 90, 140, 64, 35], "D": [70, 200, 45, 133, 64]}
 ATOL = {"float32": 2e-5, "bfloat16": 4e-2}
 
 
@@ -80,7 +80,7 @@ def with_positions(steps):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
 def test_replay_matches_plain_model(setups, tmp_path, name, cut, dtype):
     d, cfg, reqs, oracle = setups[name]
     steps = traces.mixed(reqs, seed=4) if cut == "mixed" else getattr(traces, cut)(reqs)

@@ -19,10 +19,18 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=4, hidden_si
               num_key_value_heads=3, head_dim=48, intermediate_size=100, vocab_size=301, rope_theta=500000.0,
               rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=768, hidden_act="silu",
               use_sliding_window=True, sliding_window=21, max_window_layers=2, bos_token_id=0, eos_token_id=5)
+# D has a head size the tensor-core attention kernels take (64), so the engine-level
+# tests in bfloat16 run those kernels; one of its layers has a window.
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_size=136, num_attention_heads=6,
+              num_key_value_heads=2, head_dim=64, intermediate_size=200, vocab_size=384, rope_theta=50000.0,
+              rms_norm_eps=2e-6, tie_word_embeddings=True, max_position_embeddings=2048, hidden_act="silu",
+              sliding_window=70, layer_types=["full_attention", "sliding_attention", "full_attention"],
+              bos_token_id=0, eos_token_id=4)
 INIT = {"A": dict(sigma=0.02, gain_jitter=0.1), "B": dict(sigma=0.03, gain_jitter=0.2),
-        "C": dict(sigma=0.05, gain_jitter=0.15)}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-PAGE_SIZES = {"A": 4, "B": 8, "C": 16}
+        "C": dict(sigma=0.05, gain_jitter=0.15),
+        "D": dict(sigma=0.04, gain_jitter=0.1)}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 16}
 
 
 def make_model_dir(name: str, seed: int = 0, root: str = None, **init) -> str:
