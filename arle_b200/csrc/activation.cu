@@ -16,6 +16,29 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   }
 }
 
+// Eight elements per thread and step for bfloat16 rows whose width is a multiple of 8.
+__global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inter,
+                                         size_t total8) {
+  const int i8 = inter >> 3;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / i8;
+    const int c = (int)(idx - t * i8);
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter + 8 * c);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter + inter + 8 * c);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float ga = __low2float(g2[k]), gb = __high2float(g2[k]);
+      o2[k] = __floats2bfloat162_rn(ga / (1.0f + expf(-ga)) * __low2float(u2[k]),
+                                    gb / (1.0f + expf(-gb)) * __high2float(u2[k]));
+    }
+    *reinterpret_cast<uint4*>(out + t * (size_t)inter + 8 * c) = o4;
+  }
+}
+
 ARLE_API int arle_silu_mul(const void* gu, void* out, int dtype, int num_tokens, int inter, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
   if (inter <= 0) return ARLE_E_BADARG;
@@ -23,6 +46,13 @@ ARLE_API int arle_silu_mul(const void* gu, void* out, int dtype, int num_tokens,
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 32) blocks = 148 * 32;
+  if (dtype == 1 && inter % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    const size_t total8 = total / 8;
+    size_t b8 = (total8 + threads - 1) / threads;
+    if (b8 > 148 * 32) b8 = 148 * 32;
+    silu_mul_bf16_vec_kernel<<<(int)b8, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total8);
+    return launch_status();
+  }
   if (dtype == 0)
     silu_mul_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)out, inter, total);
   else if (dtype == 1)

@@ -14,9 +14,10 @@
 //   rounded to bfloat16 for P.V as in cklxx/arle's decode kernel
 //   (crates/cuda-kernels/tools/tilelang/batch_decode_paged_hd128.py:134-231).
 //   The four warps' partial results are merged in shared memory; with more than
-//   one split the CTA writes an unnormalised partial (o, m, l) and a small merge
-//   kernel combines the splits (FlashDecoding, as the reference's split-KV
-//   variant does, :239-463).
+//   one split the CTA writes an unnormalised partial (o, m, l), and the split that
+//   finishes last (a counter per request and kv head) combines them in the same
+//   launch (FlashDecoding; the reference's split-KV variant uses a second kernel,
+//   :239-463).
 // Rows whose step entry has more than one token are skipped (the prefill kernel
 // takes them).  The key range of a row is [max(0, kv_len - window), kv_len).
 #include "common.cuh"
@@ -33,8 +34,8 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
-    int bt_stride, float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int page_size,
-    float scale_log2, int window, int splits) {
+    int bt_stride, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nq, int nkv,
+    int page_size, float scale_log2, int window, int splits) {
   constexpr int ROW = HD + 8;                 // padded row, in elements: 16 B more keeps ldmatrix conflict-free
   constexpr int CHUNKS = HD / 8;              // 16-byte chunks per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -55,14 +56,14 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
 
-  if (beg >= end) {                            // nothing for this split: an empty partial
-    if (splits > 1 && tid < G) {
+  const bool empty = beg >= end;               // nothing for this split: it publishes an empty partial
+  if (empty) {
+    if (tid < G) {
       float* ml = part_ml + (((size_t)r * nq + kvh * G + tid) * splits + split) * 2;
       ml[0] = -INFINITY;
       ml[1] = 0.f;
     }
-    return;
-  }
+  } else {
   const int* bt = block_table + (size_t)r * bt_stride;
   const size_t head_stride = (size_t)page_size * HD;
   const size_t page_stride = (size_t)nkv * head_stride;
@@ -228,38 +229,60 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
       }
     }
   }
-}
+  }  // !empty
+  if (splits == 1) return;
 
-// out[t, head, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the splits.
-template <int HD>
-__global__ void paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                          const int* __restrict__ q_indptr, __nv_bfloat16* __restrict__ out, int nq,
-                                          int splits) {
-  const int r = blockIdx.x, head = blockIdx.y;
-  const int t = q_indptr[r];
-  if (q_indptr[r + 1] - t != 1) return;
-  const size_t base = ((size_t)r * nq + head) * splits;
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float L = 0.f, O = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float l = part_ml[(base + s) * 2 + 1];
-      if (l > 0.f) {
-        const float f = exp2f(part_ml[(base + s) * 2] - M);
-        L += l * f;
-        O += part_o[(base + s) * HD + d] * f;
-      }
+  // The split that arrives last combines all of them:
+  //   out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),  M = max_s m_s.
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int prev = atomicAdd(&counters[r * nkv + kvh], 1);
+    is_last = prev == splits - 1;
+    if (is_last) counters[r * nkv + kvh] = 0;            // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float* fac = reinterpret_cast<float*>(smem_raw);        // [G][splits] factors, then [G] 1 / L
+  float* invl = fac + 16 * 64;
+  for (int i = tid; i < G * splits; i += kThreads) {
+    const int row = i / splits, sp = i % splits;
+    fac[row * 64 + sp] = __ldcg(part_ml + (((size_t)r * nq + kvh * G + row) * splits + sp) * 2);
+  }
+  __syncthreads();
+  if (tid < G) {
+    float M = -INFINITY;
+    for (int sp = 0; sp < splits; ++sp) M = fmaxf(M, fac[tid * 64 + sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float l = __ldcg(part_ml + (((size_t)r * nq + kvh * G + tid) * splits + sp) * 2 + 1);
+      const float f = l > 0.f ? exp2f(fac[tid * 64 + sp] - M) : 0.f;
+      fac[tid * 64 + sp] = f;
+      L += l * f;
     }
-    out[((size_t)t * nq + head) * HD + d] = __float2bfloat16_rn(O / L);
+    invl[tid] = 1.0f / L;
+  }
+  __syncthreads();
+  for (int i = tid; i < G * HD; i += kThreads) {
+    const int row = i / HD, d = i % HD;
+    const float* po = part_o + ((size_t)r * nq + kvh * G + row) * splits * HD + d;
+    float O = 0.f;
+#pragma unroll 4
+    for (int sp = 0; sp < splits; ++sp) {
+      const float f = fac[row * 64 + sp];
+      if (f > 0.f) O += __ldcg(po + (size_t)sp * HD) * f;
+    }
+    out[((size_t)t * nq + kvh * G + row) * HD + d] = __float2bfloat16_rn(O * invl[row]);
   }
 }
 
 template <int HD>
 int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cache, const void* v_cache,
                   const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, float* part_o,
-                  float* part_ml, int nq, int nkv, int page_size, float scale, int window, int rows, int splits,
-                  cudaStream_t s) {
+                  float* part_ml, int* counters, int nq, int nkv, int page_size, float scale, int window, int rows,
+                  int splits, cudaStream_t s) {
   constexpr int ROW = HD + 8;
   const size_t tiles = (size_t)(4 * kTile + 16) * ROW * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)(4 * 16 * HD + 128) * sizeof(float);
@@ -273,33 +296,30 @@ int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cach
   dim3 grid(rows, nkv, splits);
   paged_decode_kernel<HD><<<grid, kThreads, smem, s>>>(
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
-      (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, nq, nkv, page_size,
-      scale * 1.4426950408889634f, window, splits);
-  int rc = launch_status();
-  if (rc != 0 || splits == 1) return rc;
-  paged_decode_merge_kernel<HD><<<dim3(rows, nq), HD < 128 ? HD : 128, 0, s>>>(part_o, part_ml, q_indptr,
-                                                                              (__nv_bfloat16*)out, nq, splits);
+      (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters, nq, nkv,
+      page_size, scale * 1.4426950408889634f, window, splits);
   return launch_status();
 }
 
 }  // namespace
 
-// Scratch: part_o float32 [rows * nq * splits * hd], part_ml float32 [rows * nq * splits * 2]; unused when splits == 1.
+// Scratch when splits > 1: part_o float32 [rows * nq * splits * hd], part_ml float32 [rows * nq * splits * 2],
+// and counters int32 [rows * nkv] that must be zero before the first launch (the kernel leaves them zero).
 ARLE_API int arle_paged_attention_decode(const void* q, int q_row_stride, void* out, const void* k_cache,
                                          const void* v_cache, const int* q_indptr, const int* kv_lens,
-                                         const int* block_table, int bt_stride, float* part_o, float* part_ml, int nq,
-                                         int nkv, int hd, int page_size, float scale, int window, int rows, int splits,
-                                         cudaStream_t s) {
+                                         const int* block_table, int bt_stride, float* part_o, float* part_ml,
+                                         int* counters, int nq, int nkv, int hd, int page_size, float scale, int window,
+                                         int rows, int splits, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || page_size <= 0) return ARLE_E_UNSUPPORTED;
-  if (splits < 1 || splits > 65535 || nkv > 65535) return ARLE_E_UNSUPPORTED;
-  if (splits > 1 && (!part_o || !part_ml)) return ARLE_E_BADARG;
+  if (splits < 1 || splits > 64 || nkv > 65535) return ARLE_E_UNSUPPORTED;
+  if (splits > 1 && (!part_o || !part_ml || !counters)) return ARLE_E_BADARG;
   if ((q_row_stride % 8) != 0) return ARLE_E_UNSUPPORTED;     // 16-byte loads of q rows
   if (hd == 128)
     return launch_decode<128>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o,
-                              part_ml, nq, nkv, page_size, scale, window, rows, splits, s);
+                              part_ml, counters, nq, nkv, page_size, scale, window, rows, splits, s);
   if (hd == 64)
     return launch_decode<64>(q, q_row_stride, out, k_cache, v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o,
-                             part_ml, nq, nkv, page_size, scale, window, rows, splits, s);
+                             part_ml, counters, nq, nkv, page_size, scale, window, rows, splits, s);
   return ARLE_E_UNSUPPORTED;
 }

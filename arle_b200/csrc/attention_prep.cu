@@ -84,6 +84,92 @@ __global__ void attention_prep_kernel(T* __restrict__ qkv, int row_stride,
   }
 }
 
+// Head sizes 64 and 128 with whole-head rotation, bfloat16: every lane keeps
+// hd/32 consecutive elements in registers (one 4- or 8-byte access), the norm's
+// sum is a warp reduction and the rotation partner (element i +- hd/2) lives in
+// lane ^ 16, so no shared memory is touched.  Same arithmetic as the general
+// kernel.
+template <int HD>
+__global__ void attention_prep_bf16_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride,
+                                           const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+                                           const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                           float eps, const float* __restrict__ inv_freq,
+                                           __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                           int nq, int nkv, int page_size, int num_tokens) {
+  constexpr int VE = HD / 32;                   // elements per lane: 2 or 4
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long unit = (long long)blockIdx.x * kPrepWarps + w;
+  if (unit >= (long long)num_tokens * heads) return;
+  const int t = (int)(unit / heads), h = (int)(unit % heads);
+  __nv_bfloat16* src = qkv + (size_t)t * row_stride + (size_t)h * HD + lane * VE;
+  const int kind = h < nq ? 0 : (h < nq + nkv ? 1 : 2);
+  const int kvh = kind == 1 ? h - nq : h - nq - nkv;
+  size_t cache_at = 0;
+  bool store = false;
+  if (kind != 0) {
+    const int slot = slot_mapping[t];
+    if (slot >= 0) {
+      const int page = slot / page_size, off = slot - page * page_size;
+      cache_at = (((size_t)page * nkv + kvh) * page_size + off) * HD + lane * VE;
+      store = true;
+    }
+  }
+  uint32_t raw[VE / 2];
+  if (VE == 4) {
+    const uint2 u = *reinterpret_cast<const uint2*>(src);
+    raw[0] = u.x;
+    raw[VE / 2 - 1] = u.y;
+  } else {
+    raw[0] = *reinterpret_cast<const uint32_t*>(src);
+  }
+  if (kind == 2) {
+    if (store) {
+      if (VE == 4) *reinterpret_cast<uint2*>(v_cache + cache_at) = make_uint2(raw[0], raw[VE / 2 - 1]);
+      else *reinterpret_cast<uint32_t*>(v_cache + cache_at) = raw[0];
+    }
+    return;
+  }
+  float x[VE];
+#pragma unroll
+  for (int i = 0; i < VE / 2; ++i) {
+    const __nv_bfloat162 p = *reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+    x[2 * i] = __low2float(p);
+    x[2 * i + 1] = __high2float(p);
+  }
+  const float* wt = kind == 0 ? q_weight : k_weight;
+  if (wt) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VE; ++i) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int i = 0; i < VE; ++i) x[i] = x[i] * inv * wt[lane * VE + i];
+  }
+  const float pos = (float)positions[t];
+  float o[VE];
+#pragma unroll
+  for (int i = 0; i < VE; ++i) {
+    const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+    const int fi = (lane & 15) * VE + i;        // index of the pair
+    float sn, cs;
+    sincosf(pos * inv_freq[fi], &sn, &cs);
+    o[i] = lane < 16 ? x[i] * cs - other * sn : other * sn + x[i] * cs;
+  }
+  uint32_t packed[VE / 2];
+#pragma unroll
+  for (int i = 0; i < VE / 2; ++i) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+    packed[i] = *reinterpret_cast<uint32_t*>(&p);
+  }
+  __nv_bfloat16* dst = kind == 0 ? src : (store ? k_cache + cache_at : nullptr);
+  if (dst) {
+    if (VE == 4) *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[VE / 2 - 1]);
+    else *reinterpret_cast<uint32_t*>(dst) = packed[0];
+  }
+}
+
 ARLE_API int arle_attention_prep(void* qkv, int dtype, int row_stride, const int* positions,
                                  const int* slot_mapping, const float* q_weight, const float* k_weight,
                                  float eps, const float* inv_freq, int rotary_dim, void* k_cache,
@@ -97,6 +183,18 @@ ARLE_API int arle_attention_prep(void* qkv, int dtype, int row_stride, const int
   const long long units = (long long)num_tokens * (nq + 2 * nkv);
   const long long blocks = (units + kPrepWarps - 1) / kPrepWarps;
   if (blocks > 0x7fffffffLL) return ARLE_E_UNSUPPORTED;
+  if (dtype == 1 && (hd == 64 || hd == 128) && rotary_dim == hd && row_stride % 4 == 0 && ((uintptr_t)qkv & 7) == 0 &&
+      ((uintptr_t)k_cache & 7) == 0 && ((uintptr_t)v_cache & 7) == 0) {
+    if (hd == 128)
+      attention_prep_bf16_kernel<128><<<(int)blocks, kPrepWarps * 32, 0, s>>>(
+          (__nv_bfloat16*)qkv, row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq,
+          (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, page_size, num_tokens);
+    else
+      attention_prep_bf16_kernel<64><<<(int)blocks, kPrepWarps * 32, 0, s>>>(
+          (__nv_bfloat16*)qkv, row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq,
+          (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, page_size, num_tokens);
+    return launch_status();
+  }
   if (dtype == 0)
     attention_prep_kernel<float><<<(int)blocks, kPrepWarps * 32, 0, s>>>(
         (float*)qkv, row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim,

@@ -21,11 +21,35 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
 }
 
+// Eight table elements per thread and step (16-byte loads of bfloat16 rows).
+__global__ void embedding_bf16_vec_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                          float* __restrict__ out, int hidden, int vocab, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0 && err) atomicExch(err, 1);
+  const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)(bad ? 0 : id) * hidden);
+  float4* o = reinterpret_cast<float4*>(out + (size_t)t * hidden);
+  for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) {
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (!bad) u = row[c];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    o[2 * c] = make_float4(__low2float(h[0]), __high2float(h[0]), __low2float(h[1]), __high2float(h[1]));
+    o[2 * c + 1] = make_float4(__low2float(h[2]), __high2float(h[2]), __low2float(h[3]), __high2float(h[3]));
+  }
+}
+
 ARLE_API int arle_embedding(const int* ids, const void* table, int table_dtype, float* out,
                             int num_tokens, int hidden, int vocab, int* err, cudaStream_t s) {
   if (num_tokens <= 0) return 0;
   if (hidden <= 0 || vocab <= 0) return ARLE_E_BADARG;
   const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == 1 && hidden % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    int th = hidden / 8;
+    th = th <= 32 ? 32 : (th <= 64 ? 64 : (th <= 128 ? 128 : (th <= 256 ? 256 : 512)));
+    embedding_bf16_vec_kernel<<<num_tokens, th, 0, s>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, err);
+    return launch_status();
+  }
   if (table_dtype == 0)
     embedding_kernel<float><<<num_tokens, threads, 0, s>>>(ids, (const float*)table, out, hidden, vocab, err);
   else if (table_dtype == 1)

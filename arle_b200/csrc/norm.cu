@@ -36,9 +36,81 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__
     o[c] = from_f32<TA>(xs[c] * inv * weight[c]);
 }
 
+// Four elements per thread and step through 16-byte (float) / 8-byte (bfloat16)
+// accesses, the row kept in registers: the same arithmetic in the same order per
+// element, a fraction of the memory instructions.  Needs hidden % 4 == 0,
+// hidden <= 4 * kVecMax * blockDim.x, and 16-byte aligned rows.
+constexpr int kVecMax = 4;
+
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TA>
+__global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+                                   const int* __restrict__ rows, const float* __restrict__ weight,
+                                   TA* __restrict__ out, int hidden, float eps, int write_resid) {
+  __shared__ float red[33];
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float* xr = resid + (size_t)r * hidden;
+  const TA* dr = delta ? delta + (size_t)r * hidden : nullptr;
+  const int n4 = hidden >> 2;
+  float4 x[kVecMax];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kVecMax; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < n4) {
+      float4 v = load4(xr + 4 * c);
+      if (dr) {
+        const float4 d = load4(dr + 4 * c);
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        if (write_resid) store4(xr + 4 * c, v);
+      }
+      x[k] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  }
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  TA* o = out + (size_t)i * hidden;
+#pragma unroll
+  for (int k = 0; k < kVecMax; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < n4) {
+      const float4 w = load4(weight + 4 * c);
+      store4(o + 4 * c, make_float4(x[k].x * inv * w.x, x[k].y * inv * w.y, x[k].z * inv * w.z, x[k].w * inv * w.w));
+    }
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 template <typename TA>
 static int launch(float* resid, const void* delta, const int* rows, const float* weight, void* out,
                   int n_out, int hidden, float eps, int write_resid, cudaStream_t s) {
+  if (hidden % 4 == 0 && hidden <= 4 * kVecMax * 1024 && aligned16(resid) && aligned16(weight) && aligned16(out) &&
+      aligned16(delta)) {
+    const int n4 = hidden / 4;
+    int threads = (n4 + kVecMax - 1) / kVecMax;
+    threads = threads <= 64 ? 64 : (threads <= 128 ? 128 : (threads <= 256 ? 256 : (threads <= 512 ? 512 : 1024)));
+    rmsnorm_vec_kernel<TA><<<n_out, threads, 0, s>>>(resid, (const TA*)delta, rows, weight, (TA*)out, hidden, eps,
+                                                     write_resid);
+    return launch_status();
+  }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return ARLE_E_UNSUPPORTED;

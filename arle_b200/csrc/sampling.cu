@@ -178,6 +178,69 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
   }
 }
 
+// Greedy rows only, large vocabularies: the row is cut into kArgmaxParts parts that
+// are searched by separate blocks, then one small block per row picks the best
+// part (ties: the lowest index, as everywhere).
+constexpr int kArgmaxParts = 32;
+
+__global__ void __launch_bounds__(kSampleThreads) argmax_part_kernel(const float* __restrict__ logits, int ld, int vocab,
+                                                                     float* __restrict__ part_val, int* __restrict__ part_idx) {
+  __shared__ float sval[kSampleThreads];
+  __shared__ int sidx[kSampleThreads];
+  const int row = blockIdx.y, part = blockIdx.x;
+  const int per = (vocab + kArgmaxParts - 1) / kArgmaxParts;
+  const int b = part * per, e = min(vocab, b + per);
+  const float* x = logits + (size_t)row * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
+    const float v = x[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  sval[threadIdx.x] = best;
+  sidx[threadIdx.x] = bi;
+  __syncthreads();
+  for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
+    if (threadIdx.x < s) {
+      const float v = sval[threadIdx.x + s];
+      const int i = sidx[threadIdx.x + s];
+      if (v > sval[threadIdx.x] || (v == sval[threadIdx.x] && i < sidx[threadIdx.x])) { sval[threadIdx.x] = v; sidx[threadIdx.x] = i; }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    part_val[row * kArgmaxParts + part] = sval[0];
+    part_idx[row * kArgmaxParts + part] = sidx[0];
+  }
+}
+
+__global__ void argmax_pick_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int* __restrict__ out) {
+  const int row = blockIdx.x, lane = threadIdx.x;       // one warp, kArgmaxParts == 32
+  float v = part_val[row * kArgmaxParts + lane];
+  int i = part_idx[row * kArgmaxParts + lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+  if (lane == 0) out[row] = i == 0x7fffffff ? 0 : i;
+}
+
+// All rows greedy.  scratch: float32 [rows * 64] (values in the first half, indices in the second).
+ARLE_API int arle_argmax(const float* logits, int ld, int rows, int vocab, float* scratch, int* out, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || ld < vocab || !scratch) return ARLE_E_BADARG;
+  if (rows > 65535) return ARLE_E_UNSUPPORTED;
+  float* pv = scratch;
+  int* pi = reinterpret_cast<int*>(scratch + (size_t)rows * kArgmaxParts);
+  argmax_part_kernel<<<dim3(kArgmaxParts, rows), kSampleThreads, 0, s>>>(logits, ld, vocab, pv, pi);
+  int rc = launch_status();
+  if (rc) return rc;
+  argmax_pick_kernel<<<rows, 32, 0, s>>>(pv, pi, out);
+  return launch_status();
+}
+
 ARLE_API int arle_sample(const float* logits, int ld, int rows, int vocab, const float* temperature,
                          const int* top_k, const float* top_p, const float* min_p, const float* uniform,
                          float* scratch, int* out, cudaStream_t s) {

@@ -46,6 +46,21 @@ class Workspace:
             self._bufs[key] = buf
         return buf[:n].view(shape)
 
+    def get_zeroed(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Like ``get``, but the buffer is zero when it is first handed out (and after it
+        had to grow).  For flags and counters that kernels leave at zero."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            if self.frozen:
+                raise RuntimeError(f"workspace buffer '{name}' would have to grow inside a captured graph")
+            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(shape)
+
     def nbytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
 

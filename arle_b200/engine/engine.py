@@ -143,6 +143,9 @@ class Engine:
                         on_token(r.rid, t)
                     seen[r.rid] = len(r.output)
         self.scheduler.finished.clear()
+        if torch.device(self.options.device).type == "cuda":
+            from .. import ops
+            ops.check_errors(self.options.device)
         return [GenerationOutput(r.rid, r.prompt, list(r.output), r.finish_reason, r.preemptions) for r in reqs]
 
     def stats(self) -> dict:

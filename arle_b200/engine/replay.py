@@ -70,6 +70,7 @@ def main(argv=None) -> int:
         for rid in rec.get("end", ()):
             runner.end_request(rid)
         print(f"done {step}", flush=True)
+    ops.check_errors(args.device)
     return 0
 
 

@@ -42,9 +42,12 @@ _SIGNATURES = {
     "arle_silu_mul": [_P, _P, _I, _I, _I, _P],
     "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
-    "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "arle_gemm_skinny": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+    "arle_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+    "arle_argmax": [_P, _I, _I, _I, _P, _P, _P],
     "arle_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
 }
 
@@ -65,6 +68,27 @@ def library() -> ctypes.CDLL:
             fn.restype = c_int
         _LIB = lib
     return _LIB
+
+
+_ERR_FLAGS = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """The device word that kernels with bounded waits raise when a wait ran out
+    (one int32 per device, made at first use)."""
+    key = torch.device(device)
+    if key not in _ERR_FLAGS:
+        _ERR_FLAGS[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _ERR_FLAGS[key]
+
+
+def check_errors(device) -> None:
+    """Reads the error word (a device synchronisation) and raises if a kernel gave
+    up waiting; the word is cleared."""
+    key = torch.device(device)
+    if key in _ERR_FLAGS and int(_ERR_FLAGS[key].item()) != 0:
+        _ERR_FLAGS[key].zero_()
+        raise KernelError("a kernel gave up a bounded wait (asynchronous copy did not complete); results are invalid")
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -165,12 +189,44 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm: bfloat16 path needs bfloat16 operands, got {x.dtype} and {w.dtype}")
     _ptr(x), _ptr(w), _ptr(out)
+    if skinny_gemm_supported(x, w, out):
+        _check(library().arle_gemm_skinny(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out), out.stride(0),
+                                          M, N, K, _ptr(error_flag(x.device)), _stream()), "gemm_skinny")
+        return
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     elif out.dtype == torch.float32:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
         raise KernelError(f"gemm: output type {out.dtype}")
+
+
+def tcgen05_gemm_supported(x, w, out) -> bool:
+    """The tcgen05 kernel takes bfloat16 operands with K and the row strides multiples
+    of 8 elements and 16-byte aligned bases (what its TMA tensor maps need)."""
+    K = x.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(1) == 1
+            and w.stride(1) == 1 and out.stride(1) == 1 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.dtype in (torch.bfloat16, torch.float32))
+
+
+def gemm_tcgen05(x, w, out) -> None:
+    """out[M, N] = x[M, K] . w[N, K]^T on the tcgen05 tensor cores (TMA-fed, TMEM accumulators)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N or not tcgen05_gemm_supported(x, w, out):
+        raise KernelError(f"gemm_tcgen05: unsupported operands x {tuple(x.shape)} w {tuple(w.shape)} out {tuple(out.shape)}")
+    _check(library().arle_gemm_tcgen05(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out), out.stride(0), M, N,
+                                       K, _ptr(error_flag(x.device)), _stream()), "gemm_tcgen05")
+
+
+def skinny_gemm_supported(x, w, out) -> bool:
+    """The weight-streaming kernel takes up to 8 rows of x (the kernel itself up to 16, where cuBLAS is faster), K a multiple of 32, rows
+    that start on 16-byte boundaries and unit inner strides."""
+    M, K = x.shape
+    return (M <= 8 and K % 32 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and out.dtype in (torch.bfloat16, torch.float32))
 
 
 # ------------------------------------------------------------------- attention
@@ -231,12 +287,13 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
                                     page_size, scale, window, batch.max_q_len, skip_single=batch.num_single > 0)
         if batch.num_single > 0:
             splits = decode_splits(batch.num_rows, nkv, block_table.shape[1] * page_size)
-            part_o = part_ml = None
+            part_o = part_ml = counters = None
             if splits > 1:
                 part_o = batch.ws.get("attn_part_o", (batch.num_rows * nq * splits * hd,), torch.float32)
                 part_ml = batch.ws.get("attn_part_ml", (batch.num_rows * nq * splits * 2,), torch.float32)
+                counters = batch.ws.get_zeroed("attn_split_counters", (batch.num_rows * nkv,), torch.int32)
             paged_attention_decode(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd,
-                                   page_size, scale, window, splits, part_o, part_ml)
+                                   page_size, scale, window, splits, part_o, part_ml, counters)
         return
     _check(library().arle_paged_attention_plain(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _dt(q), _ptr(positions), _ptr(row_of_token),
@@ -253,30 +310,33 @@ def fast_attention_supported(q, nq: int, nkv: int, hd: int) -> bool:
 
 
 def decode_splits(rows: int, nkv: int, kv_bound: int) -> int:
-    """Splits along the keys so that about three CTAs per SM are in flight, never
-    more than one per 64-key tile of the longest request the tables allow."""
-    target = 148 * 3
-    splits = -(-target // max(1, rows * nkv))
+    """Splits along the keys.  With enough work for four waves of CTAs (three CTAs
+    per SM), one split per 512 keys; otherwise as many splits as fill one wave.
+    Never more than one per 64-key tile of the longest request the tables allow."""
+    slots = 148 * 3
+    base = max(1, rows * nkv)
+    by_len = -(-kv_bound // 512)
+    splits = by_len if base * by_len >= 4 * slots else max(1, slots // base)
     return max(1, min(splits, -(-kv_bound // 64), 64))
 
 
 def paged_attention_decode(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
-                           window, splits: int, part_o=None, part_ml=None) -> None:
+                           window, splits: int, part_o=None, part_ml=None, counters=None) -> None:
     """Split-KV attention of the rows that have exactly one query (others are
     skipped).  q_indptr int32 [R+1], kv_lens int32 [R] (keys after this step).
-    part_o / part_ml: float32 scratch of R*nq*splits*hd and R*nq*splits*2 elements
-    when splits > 1."""
+    When splits > 1: part_o / part_ml are float32 scratch of R*nq*splits*hd and
+    R*nq*splits*2 elements, counters int32 [R*nkv] that is zero before the first
+    launch (the kernel leaves it zero)."""
     R = kv_lens.numel()
-    if splits > 1 and (part_o is None or part_ml is None or part_o.numel() < R * nq * splits * hd
-                       or part_ml.numel() < R * nq * splits * 2 or part_o.dtype != torch.float32):
+    if splits > 1 and (part_o is None or part_ml is None or counters is None or part_o.numel() < R * nq * splits * hd
+                       or part_ml.numel() < R * nq * splits * 2 or part_o.dtype != torch.float32
+                       or counters.dtype != torch.int32 or counters.numel() < R * nkv):
         raise KernelError("paged_attention_decode: scratch for the splits is missing or too small")
     _i32(q_indptr, "q_indptr"), _i32(kv_lens, "kv_lens"), _i32(block_table, "block_table")
     _check(library().arle_paged_attention_decode(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(q_indptr), _ptr(kv_lens),
-        _ptr(block_table), block_table.stride(0), _ptr(part_o), _ptr(part_ml), nq, nkv, hd, page_size, float(scale),
-        int(window) if window else 0, R, int(splits), _stream()), "paged_attention_decode")
-    if splits > 1:
-        add_launches(1)
+        _ptr(block_table), block_table.stride(0), _ptr(part_o), _ptr(part_ml), _ptr(counters), nq, nkv, hd, page_size,
+        float(scale), int(window) if window else 0, R, int(splits), _stream()), "paged_attention_decode")
 
 
 def paged_attention_prefill(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
@@ -301,6 +361,18 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 
 # -------------------------------------------------------------------- sampling
+def argmax(logits, scratch, out) -> None:
+    """out[r] = index of the largest logit of row r (ties: the lowest index), float32
+    logits [R, V]; scratch float32 [R * 64]."""
+    R, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32 or out.numel() < R:
+        raise KernelError("argmax: float32 logits with unit inner stride, int32 out with one entry per row")
+    if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < R * 64:
+        raise KernelError("argmax: scratch must be float32 with 64 entries per row")
+    _check(library().arle_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(scratch), _ptr(out), _stream()), "argmax")
+    add_launches(1)
+
+
 def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out) -> None:
     """out[r] = next token of row r from float32 logits [R, V].  Per-row device
     arrays: temperature float32 (<= 0: greedy), top_k int32 (<= 0 off), top_p

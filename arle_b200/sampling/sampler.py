@@ -28,7 +28,7 @@ class Sampler:
         self.device = torch.device(device)
         self._scratch: Optional[torch.Tensor] = None
         self._out: Optional[torch.Tensor] = None
-        self._par: Optional[torch.Tensor] = None
+        self._argmax_scratch: Optional[torch.Tensor] = None
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[random.Random]) -> List[int]:
         """logits float32 [R, vocab] on the device; returns R token ids on the host."""
@@ -37,7 +37,9 @@ class Sampler:
             self._out = torch.empty(max(R, 64), dtype=torch.int32, device=self.device)
         out = self._out[:R]
         if all(p.is_greedy() for p in params):
-            ops.sample(logits, None, None, None, None, None, None, out)
+            if self._argmax_scratch is None or self._argmax_scratch.numel() < R * 64:
+                self._argmax_scratch = torch.empty(max(R, 64) * 64, dtype=torch.float32, device=self.device)
+            ops.argmax(logits, self._argmax_scratch, out)
             return out.tolist()
         if self._scratch is None or self._scratch.numel() < R * self.vocab:
             self._scratch = torch.empty(R * self.vocab, dtype=torch.float32, device=self.device)

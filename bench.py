@@ -98,6 +98,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than Qwen3-8B's 36 (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="profiling aid: run only the decode steps at --batch, or only the prefill")
     ap.add_argument("--no-cuda-graph", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -170,14 +172,19 @@ def main() -> int:
             runner.end_request(r)
         return ms, launches, ctx_mid
 
+    if args.only == "decode":
+        ms, launches, _ = decode_run(args.batch, args.steps, args.warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
+                          "gpu_launches": int(launches)}))
+        return 0
     clocks = ClockSampler()
-    ms, launches, ctx_mid = decode_run(args.batch, args.steps, args.warmup, clocks)
+    ms, launches, ctx_mid = (0.0, 0, CONTEXT) if args.only == "prefill" else decode_run(args.batch, args.steps, args.warmup, clocks)
     clk = clocks.stop()
-    value = args.batch * 1000.0 / ms
+    value = args.batch * 1000.0 / ms if ms else 0.0
     step_bytes = weight_bytes + args.batch * ctx_mid * kv_bytes_per_token
-    achieved = step_bytes / (ms * 1e-3) / 1e9
+    achieved = step_bytes / (ms * 1e-3) / 1e9 if ms else 0.0
     points = {}
-    for b in (1, 64):
+    for b in (() if args.only == "prefill" else (1, 64)):
         m, _, _ = decode_run(b, max(8, args.steps // 2), args.warmup)
         points[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
 
@@ -194,9 +201,12 @@ def main() -> int:
         runner.end_request(rid)
         return e0.elapsed_time(e1)
 
-    for i in range(3):
+    for i in range(1 if args.only == "prefill" else 3):
         prefill_once(f"w{i}")
-    pf_ms = sorted(prefill_once(f"t{i}") for i in range(5))[2]
+    pf_ms = sorted(prefill_once(f"t{i}") for i in range(1 if args.only == "prefill" else 5))[0 if args.only == "prefill" else 2]
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", "layers": layers, "ms": round(pf_ms, 3)}))
+        return 0
     c = model.config
     mm_params = layers * (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
                           + c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)

@@ -94,6 +94,10 @@ def silu_mul(gate_up, out):
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
 
+def argmax(logits, scratch, out):
+    out[: logits.shape[0]] = torch.argmax(logits, dim=1).to(out.dtype)      # torch returns the first maximal index
+
+
 def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out):
     R, V = logits.shape
     for r in range(R):
@@ -125,4 +129,4 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out):
         out[r] = int(hit[0]) if hit.numel() else int(torch.nonzero(p > 0)[-1])
 
 
-ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "attention_prep", "paged_attention", "silu_mul", "sample")
+ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "attention_prep", "paged_attention", "silu_mul", "argmax", "sample")

@@ -129,6 +129,46 @@ def test_gemm_bf16(M, N, K):
     torch.testing.assert_close(out32, exp, rtol=1e-3, atol=1e-3)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 16, 32), (1, 4096, 4096), (8, 6144, 4096), (3, 1000, 192), (5, 37, 320),
+                                   (8, 301, 256), (7, 500, 12288), (8, 200, 12288), (8, 4100, 12288), (2, 151936, 128)])
+def test_gemm_skinny_weight_streaming(M, N, K, out_dtype):
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    assert ops.skinny_gemm_supported(x, w, torch.empty(M, N, dtype=out_dtype, device=DEV))
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm(x, w, out)
+    exp = x.double() @ w.double().t()
+    err = (out.double() - exp).abs().max().item()
+    scale = exp.abs().max().item()
+    assert err <= (2e-5 if out_dtype == torch.float32 else 6e-3) * max(scale, 1.0), (err, scale)
+    again = torch.empty_like(out)
+    ops.gemm(x, w, again)
+    assert torch.equal(out, again)              # fixed summation order: bit-identical from run to run
+    ops.check_errors(DEV)                       # no bounded wait ran out
+
+
+def test_gemm_skinny_takes_row_views():
+    big = rnd(8, 512, dtype=torch.bfloat16, seed=3)
+    x, w = big[:, :256], rnd(70, 256, dtype=torch.bfloat16, seed=4)      # row stride 512, unit inner stride
+    out = torch.empty(8, 70, dtype=torch.bfloat16, device=DEV)
+    ops.gemm(x, w, out)
+    torch.testing.assert_close(out.float(), x.float() @ w.float().t(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (256, 512, 4096), (2048, 6144, 4096), (100, 300, 72),
+                                   (1, 256, 64), (129, 257, 200), (64, 4096, 12288), (300, 1000, 136), (2048, 4096, 4096)])
+def test_gemm_tcgen05(M, N, K, out_dtype):
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_tcgen05(x, w, out)
+    ops.check_errors(DEV)
+    exp = x.double() @ w.double().t()
+    err = (out.double() - exp).abs().max().item()
+    scale = exp.abs().max().item()
+    assert err <= (3e-5 if out_dtype == torch.float32 else 6e-3) * max(scale, 1.0), (err, scale)
+
+
 def _paged_setup(dtype, nq, nkv, hd, ps, lens, q_lens, seed=0):
     """Random cache contents for requests of the given lengths, scattered pages."""
     g = torch.Generator().manual_seed(seed)
@@ -232,6 +272,19 @@ def test_sample_greedy_lowest_index_on_ties(V):
     assert out.cpu().tolist() == exp.tolist() and out[1].item() == 7 and out[2].item() == 0
 
 
+@pytest.mark.parametrize("R,V", [(1, 40), (3, 301), (9, 151936)])
+def test_argmax_split_kernel(R, V):
+    logits = rnd(R, V, seed=7)
+    logits[0, V - 1] = logits[0, 5] = 99.0
+    if R > 1:
+        logits[1] = -3.0
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, torch.empty(R * 64, device=DEV), out)
+    assert out.tolist() == torch.argmax(logits, dim=1).tolist() and out[0].item() == 5
+    if R > 1:
+        assert out[1].item() == 0
+
+
 @pytest.mark.parametrize("V", [257, 5000])
 def test_sample_temperature_top_k_top_p(V):
     R = 8
@@ -301,9 +354,13 @@ def test_decode_attention_kernel(nq, nkv, hd, ps, window, splits):
     out = torch.zeros(R, nq * hd, dtype=torch.bfloat16, device=DEV)
     po = torch.full((R * nq * splits * hd,), float("nan"), device=DEV)       # stale scratch must not leak
     pml = torch.full((R * nq * splits * 2,), float("nan"), device=DEV)
-    ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, splits, po, pml)
+    cnt = torch.zeros(R * nkv, dtype=torch.int32, device=DEV)
     exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, window)
-    torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+    for _ in range(2):                      # twice: the counters must be back at zero after a launch
+        out.zero_()
+        ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, splits, po, pml, cnt)
+        torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+        assert cnt.abs().sum().item() == 0
 
 
 @pytest.mark.parametrize("nq,nkv,hd,ps,window", [(32, 8, 128, 16, None), (6, 1, 64, 8, None), (4, 4, 128, 16, 70),
@@ -348,7 +405,8 @@ def test_fast_attention_sees_one_far_key_and_the_windows_edge(kernel):
             out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
             if kernel == "decode":
                 ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, 4,
-                                           torch.empty(nq * 4 * hd, device=DEV), torch.empty(nq * 8, device=DEV))
+                                           torch.empty(nq * 4 * hd, device=DEV), torch.empty(nq * 8, device=DEV),
+                                           torch.zeros(nkv, dtype=torch.int32, device=DEV))
             else:
                 ops.paged_attention_prefill(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, 3)
             close = (out[-1, :hd].float() - vc[page, 0, off].float()).abs().max().item() < 2e-2
