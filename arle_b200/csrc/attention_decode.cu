@@ -42,6 +42,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
   __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [2][kTile][ROW]
   __nv_bfloat16* vs = ks + 2 * kTile * ROW;                                // [2][kTile][ROW]
   __nv_bfloat16* qs = vs + 2 * kTile * ROW;                                // [16][ROW]
+  __shared__ int pgbuf[4][kTile + 1];          // page ids of four tiles in turn, fetched two tiles ahead of the data
 
   const int r = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int G = nq / nkv;
@@ -70,8 +71,21 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
   const __nv_bfloat16* kbase = k_cache + (size_t)kvh * head_stride;
   const __nv_bfloat16* vbase = v_cache + (size_t)kvh * head_stride;
 
+  // Page ids of a tile go to shared memory two tiles before its keys are fetched, so that
+  // fetching a tile does not first wait for a block-table read.
+  auto fetch_ids = [&](int tile, bool async) {
+    const int k0 = beg + tile * kTile;
+    if (k0 >= end) return;
+    const int first = k0 / page_size, last = (min(end, k0 + kTile) - 1) / page_size;
+    if (tid <= last - first) {
+      if (async) cp_async4(smem_u32(&pgbuf[tile & 3][tid]), bt + first + tid, 4);
+      else pgbuf[tile & 3][tid] = bt[first + tid];
+    }
+  };
   auto load_tile = [&](int tile, int stage) {
     const int k0 = beg + tile * kTile;
+    const int first = k0 / page_size;
+    const int* pg = pgbuf[tile & 3];
     __nv_bfloat16* kd = ks + stage * kTile * ROW;
     __nv_bfloat16* vd = vs + stage * kTile * ROW;
 #pragma unroll
@@ -82,8 +96,8 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
       const bool ok = kj < end;
       size_t off = 0;
       if (ok) {
-        const int page = bt[kj / page_size];
-        off = (size_t)page * page_stride + (size_t)(kj % page_size) * HD + part * 8;
+        const int pidx = kj / page_size;
+        off = (size_t)pg[pidx - first] * page_stride + (size_t)(kj - pidx * page_size) * HD + part * 8;
       }
       cp_async16(smem_u32(kd + key * ROW + part * 8), kbase + off, ok ? 16 : 0);
       cp_async16(smem_u32(vd + key * ROW + part * 8), vbase + off, ok ? 16 : 0);
@@ -91,6 +105,10 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
   };
 
   const int ntiles = (end - beg + kTile - 1) / kTile;
+  fetch_ids(0, false);
+  fetch_ids(1, false);
+  fetch_ids(2, false);
+  __syncthreads();
   load_tile(0, 0);
   cp_commit();
 
@@ -120,6 +138,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
     const int stage = tile & 1;
     if (tile + 1 < ntiles) {
       load_tile(tile + 1, stage ^ 1);
+      fetch_ids(tile + 3, true);
       cp_commit();
       cp_wait<1>();
     } else {

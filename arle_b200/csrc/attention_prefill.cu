@@ -25,7 +25,7 @@ constexpr int kBlockM = 64;
 constexpr int kTile = 64;
 
 template <int HD>
-__global__ void __launch_bounds__(kThreads) paged_prefill_kernel(
+__global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
@@ -35,7 +35,8 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_kernel(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [2][kTile][ROW]
   __nv_bfloat16* vs = ks + 2 * kTile * ROW;                         // [2][kTile][ROW]
-  __nv_bfloat16* qs = vs + 2 * kTile * ROW;                         // [kBlockM][ROW]
+  __nv_bfloat16* qs = ks + kTile * ROW;        // the queries pass through stage 1 of K before its first tile arrives
+  __shared__ int pgbuf[4][kTile + 1];          // page ids of four tiles in turn, fetched two tiles ahead of the data
 
   const int r = blockIdx.z, h = blockIdx.y;
   const int t0 = q_indptr[r];
@@ -59,8 +60,20 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_kernel(
   const __nv_bfloat16* kbase = k_cache + (size_t)kvh * head_stride;
   const __nv_bfloat16* vbase = v_cache + (size_t)kvh * head_stride;
 
+  auto fetch_ids = [&](int tile, bool async) {
+    const int k0 = max(lo, kb + tile * kTile);
+    const int k1 = min(p_last, kb + tile * kTile + kTile - 1);
+    if (k0 > k1) return;
+    const int first = k0 / page_size, last = k1 / page_size;
+    if (tid <= last - first) {
+      if (async) cp_async4(smem_u32(&pgbuf[tile & 3][tid]), bt + first + tid, 4);
+      else pgbuf[tile & 3][tid] = bt[first + tid];
+    }
+  };
   auto load_tile = [&](int tile, int stage) {
     const int k0 = kb + tile * kTile;
+    const int first = max(lo, k0) / page_size;
+    const int* pg = pgbuf[tile & 3];
     __nv_bfloat16* kd = ks + stage * kTile * ROW;
     __nv_bfloat16* vd = vs + stage * kTile * ROW;
 #pragma unroll
@@ -71,13 +84,17 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_kernel(
       const bool ok = kj >= lo && kj <= p_last;
       size_t off = 0;
       if (ok) {
-        const int page = bt[kj / page_size];
-        off = (size_t)page * page_stride + (size_t)(kj % page_size) * HD + part * 8;
+        const int pidx = kj / page_size;
+        off = (size_t)pg[pidx - first] * page_stride + (size_t)(kj - pidx * page_size) * HD + part * 8;
       }
       cp_async16(smem_u32(kd + key * ROW + part * 8), kbase + off, ok ? 16 : 0);
       cp_async16(smem_u32(vd + key * ROW + part * 8), vbase + off, ok ? 16 : 0);
     }
   };
+  fetch_ids(0, false);
+  fetch_ids(1, false);
+  fetch_ids(2, false);
+  __syncthreads();
   load_tile(0, 0);
   cp_commit();
 
@@ -100,6 +117,7 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_kernel(
       qa[s][3] = *reinterpret_cast<const uint32_t*>(qw + (g + 8) * ROW + s * 16 + 8 + 2 * tq);
     }
   }
+  __syncthreads();                             // every warp holds its query fragments: stage 1 may be overwritten
   // positions of this thread's two query rows; rows past the portion's end copy the last one
   const int prow0 = min(pos0 + mbeg + warp * 16 + g, p_last);
   const int prow1 = min(pos0 + mbeg + warp * 16 + g + 8, p_last);
@@ -117,6 +135,7 @@ __global__ void __launch_bounds__(kThreads) paged_prefill_kernel(
     const int stage = tile & 1;
     if (tile + 1 < ntiles) {
       load_tile(tile + 1, stage ^ 1);
+      if (tile + 3 < ntiles) fetch_ids(tile + 3, true);
       cp_commit();
       cp_wait<1>();
     } else {
@@ -219,7 +238,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, const void* k_cac
                    const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, int nq, int nkv,
                    int page_size, float scale, int window, int rows, int max_q_len, int skip_single, cudaStream_t s) {
   constexpr int ROW = HD + 8;
-  const size_t smem = (size_t)(4 * kTile + kBlockM) * ROW * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(4 * kTile) * ROW * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(paged_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -84,6 +84,12 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restri
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
   }
+  float4 wv[kVecMax];                         // fetched before the reduction so that it is not waited for after it
+#pragma unroll
+  for (int k = 0; k < kVecMax; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < n4) wv[k] = load4(weight + 4 * c);
+  }
   const float total = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
   TA* o = out + (size_t)i * hidden;
@@ -91,7 +97,7 @@ __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restri
   for (int k = 0; k < kVecMax; ++k) {
     const int c = threadIdx.x + k * blockDim.x;
     if (c < n4) {
-      const float4 w = load4(weight + 4 * c);
+      const float4 w = wv[k];
       store4(o + 4 * c, make_float4(x[k].x * inv * w.x, x[k].y * inv * w.y, x[k].z * inv * w.z, x[k].w * inv * w.w));
     }
   }
