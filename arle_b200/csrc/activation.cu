@@ -6,6 +6,8 @@ using namespace arle;
 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
@@ -19,6 +21,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 // Eight elements per thread and step for bfloat16 rows whose width is a multiple of 8.
 __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int inter,
                                          size_t total8) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i8 = inter >> 3;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / i8;
@@ -50,13 +54,13 @@ ARLE_API int arle_silu_mul(const void* gu, void* out, int dtype, int num_tokens,
     const size_t total8 = total / 8;
     size_t b8 = (total8 + threads - 1) / threads;
     if (b8 > 148 * 32) b8 = 148 * 32;
-    silu_mul_bf16_vec_kernel<<<(int)b8, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total8);
+    launch_kernel(silu_mul_bf16_vec_kernel, dim3((int)b8), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total8);
     return launch_status();
   }
   if (dtype == 0)
-    silu_mul_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)out, inter, total);
+    launch_kernel(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, 1, (const float*)gu, (float*)out, inter, total);
   else if (dtype == 1)
-    silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
+    launch_kernel(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, total);
   else
     return ARLE_E_BADARG;
   return launch_status();

@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
     int bt_stride, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nq, int nkv,
     int page_size, float scale_log2, int window, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int ROW = HD + 8;                 // padded row, in elements: 16 B more keeps ldmatrix conflict-free
   constexpr int CHUNKS = HD / 8;              // 16-byte chunks per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -313,7 +315,7 @@ int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cach
     configured = true;
   }
   dim3 grid(rows, nkv, splits);
-  paged_decode_kernel<HD><<<grid, kThreads, smem, s>>>(
+  launch_kernel(paged_decode_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 1, 
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters, nq, nkv,
       page_size, scale * 1.4426950408889634f, window, splits);

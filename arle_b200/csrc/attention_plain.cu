@@ -23,6 +23,8 @@ __global__ void paged_attention_plain_kernel(const T* __restrict__ q, int q_row_
                                              const int* __restrict__ row_of_token,
                                              const int* __restrict__ block_table, int bt_stride, int nq,
                                              int nkv, int hd, int page_size, float scale, int window) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float qs[256];
   __shared__ float acc_s[kAttnWarps][256];
   __shared__ float m_s[kAttnWarps], l_s[kAttnWarps];
@@ -109,11 +111,11 @@ ARLE_API int arle_paged_attention_plain(const void* q, int q_row_stride, void* o
   if (nq > 65535) return ARLE_E_UNSUPPORTED;
   dim3 grid(num_tokens, nq);
   if (dtype == 0)
-    paged_attention_plain_kernel<float><<<grid, kAttnWarps * 32, 0, s>>>(
+    launch_kernel(paged_attention_plain_kernel<float>, dim3(grid), dim3(kAttnWarps * 32), 0, s, 1, 
         (const float*)q, q_row_stride, (float*)out, (const float*)k_cache, (const float*)v_cache, positions,
         row_of_token, block_table, bt_stride, nq, nkv, hd, page_size, scale, window);
   else if (dtype == 1)
-    paged_attention_plain_kernel<__nv_bfloat16><<<grid, kAttnWarps * 32, 0, s>>>(
+    launch_kernel(paged_attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(kAttnWarps * 32), 0, s, 1, 
         (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
         (const __nv_bfloat16*)v_cache, positions, row_of_token, block_table, bt_stride, nq, nkv, hd,
         page_size, scale, window);

@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
     int bt_stride, int nq, int nkv, int page_size, float scale_log2, int window, int skip_single) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int ROW = HD + 8;
   constexpr int CHUNKS = HD / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -246,7 +248,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, const void* k_cac
     configured = true;
   }
   dim3 grid((max_q_len + kBlockM - 1) / kBlockM, nq, rows);
-  paged_prefill_kernel<HD><<<grid, kThreads, smem, s>>>(
+  launch_kernel(paged_prefill_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 1, 
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, nq, nkv, page_size,
       scale * 1.4426950408889634f, window, skip_single);

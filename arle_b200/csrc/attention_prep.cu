@@ -26,6 +26,8 @@ __global__ void attention_prep_kernel(T* __restrict__ qkv, int row_stride,
                                       const float* __restrict__ inv_freq, int rotary_dim,
                                       T* __restrict__ k_cache, T* __restrict__ v_cache, int nq, int nkv,
                                       int hd, int page_size, int num_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float bufs[kPrepWarps][kMaxHeadDim];
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
@@ -96,6 +98,8 @@ __global__ void attention_prep_bf16_kernel(__nv_bfloat16* __restrict__ qkv, int 
                                            float eps, const float* __restrict__ inv_freq,
                                            __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                                            int nq, int nkv, int page_size, int num_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int VE = HD / 32;                   // elements per lane: 2 or 4
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
@@ -186,21 +190,21 @@ ARLE_API int arle_attention_prep(void* qkv, int dtype, int row_stride, const int
   if (dtype == 1 && (hd == 64 || hd == 128) && rotary_dim == hd && row_stride % 4 == 0 && ((uintptr_t)qkv & 7) == 0 &&
       ((uintptr_t)k_cache & 7) == 0 && ((uintptr_t)v_cache & 7) == 0) {
     if (hd == 128)
-      attention_prep_bf16_kernel<128><<<(int)blocks, kPrepWarps * 32, 0, s>>>(
+      launch_kernel(attention_prep_bf16_kernel<128>, dim3((int)blocks), dim3(kPrepWarps * 32), 0, s, 1, 
           (__nv_bfloat16*)qkv, row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq,
           (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, page_size, num_tokens);
     else
-      attention_prep_bf16_kernel<64><<<(int)blocks, kPrepWarps * 32, 0, s>>>(
+      launch_kernel(attention_prep_bf16_kernel<64>, dim3((int)blocks), dim3(kPrepWarps * 32), 0, s, 1, 
           (__nv_bfloat16*)qkv, row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq,
           (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, page_size, num_tokens);
     return launch_status();
   }
   if (dtype == 0)
-    attention_prep_kernel<float><<<(int)blocks, kPrepWarps * 32, 0, s>>>(
+    launch_kernel(attention_prep_kernel<float>, dim3((int)blocks), dim3(kPrepWarps * 32), 0, s, 1, 
         (float*)qkv, row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim,
         (float*)k_cache, (float*)v_cache, nq, nkv, hd, page_size, num_tokens);
   else if (dtype == 1)
-    attention_prep_kernel<__nv_bfloat16><<<(int)blocks, kPrepWarps * 32, 0, s>>>(
+    launch_kernel(attention_prep_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(kPrepWarps * 32), 0, s, 1, 
         (__nv_bfloat16*)qkv, row_stride, positions, slot_mapping, q_weight, k_weight, eps, inv_freq,
         rotary_dim, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nq, nkv, hd, page_size, num_tokens);
   else

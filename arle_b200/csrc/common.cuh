@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #define ARLE_E_UNSUPPORTED (-2)
 #define ARLE_E_BADARG (-3)
 
@@ -71,6 +73,51 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   }
   __syncthreads();
   return scratch[32];
+}
+
+// Programmatic dependent launch.  Every kernel of this library starts with
+// pdl_launch_dependents() (the next kernel of the stream may be scheduled as soon as
+// all CTAs of this one have started) and calls pdl_wait() before it first touches
+// memory that an earlier kernel may have written (until then it may only set up
+// barriers and fetch weights, which no kernel writes).  Both are no-ops for a kernel
+// launched in the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// 1: kernels are launched with programmatic stream serialisation allowed.  Off by
+// default: inside captured CUDA graphs it measured slower than stream-order launches.
+inline int& pdl_enabled() {
+  static int on = 0;
+  return on;
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-launch attribute
+// (and a cluster dimension when cluster > 1).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 int cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 inline int launch_status() {

@@ -9,6 +9,8 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab,
                                  int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * hidden;
@@ -24,6 +26,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 // Eight table elements per thread and step (16-byte loads of bfloat16 rows).
 __global__ void embedding_bf16_vec_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                           float* __restrict__ out, int hidden, int vocab, int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool bad = id < 0 || id >= vocab;
@@ -47,14 +51,18 @@ ARLE_API int arle_embedding(const int* ids, const void* table, int table_dtype, 
   if (table_dtype == 1 && hidden % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     int th = hidden / 8;
     th = th <= 32 ? 32 : (th <= 64 ? 64 : (th <= 128 ? 128 : (th <= 256 ? 256 : 512)));
-    embedding_bf16_vec_kernel<<<num_tokens, th, 0, s>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, err);
+    launch_kernel(embedding_bf16_vec_kernel, dim3(num_tokens), dim3(th), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err);
     return launch_status();
   }
   if (table_dtype == 0)
-    embedding_kernel<float><<<num_tokens, threads, 0, s>>>(ids, (const float*)table, out, hidden, vocab, err);
+    launch_kernel(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const float*)table, out, hidden, vocab, err);
   else if (table_dtype == 1)
-    embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, s>>>(ids, (const __nv_bfloat16*)table, out, hidden, vocab, err);
+    launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err);
   else
     return ARLE_E_BADARG;
   return launch_status();
 }
+
+// 1: kernels are launched so that the next kernel of the stream may start its set-up
+// (barriers, weight prefetch) while the previous one finishes; 0 (default): plain launches.
+ARLE_API void arle_set_programmatic_launch(int on) { arle::pdl_enabled() = on ? 1 : 0; }

@@ -12,6 +12,8 @@ template <typename TW>
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ A, const TW* __restrict__ W,
                                                        float* __restrict__ C, int M, int N, int K, int lda,
                                                        int ldw, int ldc) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -66,9 +68,9 @@ ARLE_API int arle_gemm_f32(const float* A, const void* W, int w_dtype, float* C,
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return ARLE_E_UNSUPPORTED;
   if (w_dtype == 0)
-    gemm_f32_kernel<float><<<grid, 256, 0, s>>>(A, (const float*)W, C, M, N, K, lda, ldw, ldc);
+    launch_kernel(gemm_f32_kernel<float>, dim3(grid), dim3(256), 0, s, 1, A, (const float*)W, C, M, N, K, lda, ldw, ldc);
   else if (w_dtype == 1)
-    gemm_f32_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(A, (const __nv_bfloat16*)W, C, M, N, K, lda, ldw, ldc);
+    launch_kernel(gemm_f32_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, 1, A, (const __nv_bfloat16*)W, C, M, N, K, lda, ldw, ldc);
   else
     return ARLE_E_BADARG;
   return launch_status();

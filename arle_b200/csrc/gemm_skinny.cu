@@ -71,7 +71,7 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 template <int NT, int KB, int SLOTS, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W, int ldw, OutT* __restrict__ out,
-    int ldo, int M, int N, int K, int KS, int csize, int* __restrict__ err) {
+    int ldo, int M, int N, int K, int KS, int csize, int early, int* __restrict__ err) {
   constexpr int PITCH = KB * 2 + kRowPad;                 // bytes per weight-row segment in a stage
   constexpr int STAGE = 16 * PITCH;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + off);                              // [kWarps][SLOTS], then x's
   uint64_t* xbar = bars + kWarps * SLOTS;
 
+  pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int rank = csize > 1 ? (int)(blockIdx.x % csize) : 0;
@@ -107,13 +108,21 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
   asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   __syncwarp();
-  // this CTA's slice of x: one bulk copy per row, issued first so that it is under way
-  // while the weight ring fills; rows beyond M are zeroed by hand
-  if (warp == 0 && klen > 0) {
-    if (lane == 0) mbar_expect_tx(smem_u32(xbar), (uint32_t)(min(M, NT * 8) * klen * 2));
-    __syncwarp();
-    if (lane < M && lane < NT * 8)
-      bulk_copy_g2s(smem_u32(xs + (size_t)lane * xrow), x + (size_t)lane * ldx + ks0, (uint32_t)(klen * 2), smem_u32(xbar));
+  // this CTA's slice of x: one bulk copy per row (rows beyond M are zeroed by hand)
+  auto fetch_x = [&]() {
+    if (warp == 0 && klen > 0) {
+      if (lane == 0) mbar_expect_tx(smem_u32(xbar), (uint32_t)(min(M, NT * 8) * klen * 2));
+      __syncwarp();
+      if (lane < M && lane < NT * 8)
+        bulk_copy_g2s(smem_u32(xs + (size_t)lane * xrow), x + (size_t)lane * ldx + ks0, (uint32_t)(klen * 2), smem_u32(xbar));
+    }
+  };
+  // x is the output of the kernel before this one.  Launched early (programmatic launch),
+  // the kernel fills its weight ring first (no kernel writes weights), then waits for that
+  // kernel, then fetches x; launched in stream order, x goes first because it is needed first.
+  if (!early) {
+    pdl_wait();
+    fetch_x();
   }
 
   // stage number s of this CTA = (tile s / spt, K block s % spt); warp w owns s = w, w + kWarps, ...
@@ -136,6 +145,10 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
     if (s < total) issue(s, issued);
   }
 
+  if (early) {
+    pdl_wait();
+    fetch_x();
+  }
   bool timed_out = false;
   {
     const int per_row = klen / 8;
@@ -255,24 +268,24 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
   auto kern = skinny_gemm_kernel<NT, KB, SLOTS, OutT>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = csize;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
   // a persistent grid must be resident at once: as many clusters as the GPU can hold together
   int groups = sms / csize;
   if (csize > 1) {
     static int cached[9][4] = {};                       // [cluster size][NT + 2 * (out is float)]
     int& slot = cached[csize][(NT - 1) + 2 * (sizeof(OutT) == 4 ? 1 : 0)];
     if (slot == 0) {
+      cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(groups * csize);
+      cfg.blockDim = dim3(kThreads);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = s;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = csize;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
       int max_clusters = 0;
       e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
       if (e != cudaSuccess) return (int)e;
@@ -283,9 +296,8 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
   const int tiles = (N + 15) / 16;
   if (groups > tiles) groups = tiles;
   if (groups < 1) groups = 1;
-  cfg.gridDim = dim3(groups * csize);
-  e = cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, ldw, (OutT*)out, ldo, M, N, K,
-                         KS, csize, err);
+  e = launch_kernel(kern, dim3(groups * csize), dim3(kThreads), smem, s, csize, (const __nv_bfloat16*)x, ldx,
+                    (const __nv_bfloat16*)W, ldw, (OutT*)out, ldo, M, N, K, KS, csize, pdl_enabled(), err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }

@@ -122,6 +122,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
                                                                    const __grid_constant__ CUtensorMap map_w,
                                                                    OutT* __restrict__ out, int ldo, int M, int N, int K,
                                                                    int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -362,7 +364,7 @@ int launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, i
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long num_tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   const int grid = (int)(num_tiles < sms ? num_tiles : sms);      // persistent: one CTA per SM
-  kern<<<grid, kThreads, smem, s>>>(mx, mw, (OutT*)out, ldo, M, N, K, err);
+  launch_kernel(kern, dim3(grid), dim3(kThreads), smem, s, 1, mx, mw, (OutT*)out, ldo, M, N, K, err);
   return launch_status();
 }
 

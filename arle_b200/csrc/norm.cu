@@ -15,6 +15,8 @@ template <typename TA>
 __global__ void rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
                                const int* __restrict__ rows, const float* __restrict__ weight,
                                TA* __restrict__ out, int hidden, float eps, int write_resid) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float xs[];
   __shared__ float red[33];
   const int i = blockIdx.x;
@@ -62,6 +64,8 @@ template <typename TA>
 __global__ void rmsnorm_vec_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
                                    const int* __restrict__ rows, const float* __restrict__ weight,
                                    TA* __restrict__ out, int hidden, float eps, int write_resid) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[33];
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
@@ -113,7 +117,7 @@ static int launch(float* resid, const void* delta, const int* rows, const float*
     const int n4 = hidden / 4;
     int threads = (n4 + kVecMax - 1) / kVecMax;
     threads = threads <= 64 ? 64 : (threads <= 128 ? 128 : (threads <= 256 ? 256 : (threads <= 512 ? 512 : 1024)));
-    rmsnorm_vec_kernel<TA><<<n_out, threads, 0, s>>>(resid, (const TA*)delta, rows, weight, (TA*)out, hidden, eps,
+    launch_kernel(rmsnorm_vec_kernel<TA>, dim3(n_out), dim3(threads), 0, s, 1, resid, (const TA*)delta, rows, weight, (TA*)out, hidden, eps,
                                                      write_resid);
     return launch_status();
   }
@@ -125,7 +129,7 @@ static int launch(float* resid, const void* delta, const int* rows, const float*
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  rmsnorm_kernel<TA><<<n_out, threads, smem, s>>>(resid, (const TA*)delta, rows, weight, (TA*)out, hidden,
+  launch_kernel(rmsnorm_kernel<TA>, dim3(n_out), dim3(threads), smem, s, 1, resid, (const TA*)delta, rows, weight, (TA*)out, hidden,
                                                   eps, write_resid);
   return launch_status();
 }
@@ -146,6 +150,8 @@ ARLE_API int arle_rmsnorm(float* resid, const void* delta, const int* rows, cons
 // output that no norm follows directly.
 template <typename TA>
 __global__ void residual_add_kernel(float* __restrict__ resid, const TA* __restrict__ delta, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
     resid[i] += to_f32(delta[i]);
 }
@@ -156,9 +162,9 @@ ARLE_API int arle_residual_add(float* resid, const void* delta, int act_dtype, i
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (act_dtype == 0)
-    residual_add_kernel<float><<<(int)blocks, 256, 0, s>>>(resid, (const float*)delta, total);
+    launch_kernel(residual_add_kernel<float>, dim3((int)blocks), dim3(256), 0, s, 1, resid, (const float*)delta, total);
   else if (act_dtype == 1)
-    residual_add_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, s>>>(resid, (const __nv_bfloat16*)delta, total);
+    launch_kernel(residual_add_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, 1, resid, (const __nv_bfloat16*)delta, total);
   else
     return ARLE_E_BADARG;
   return launch_status();

@@ -62,6 +62,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(
     const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
     const float* __restrict__ uniform, float* __restrict__ scratch, int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[33];
   __shared__ float sval[kSampleThreads];
   __shared__ int sidx[kSampleThreads];
@@ -185,6 +187,8 @@ constexpr int kArgmaxParts = 32;
 
 __global__ void __launch_bounds__(kSampleThreads) argmax_part_kernel(const float* __restrict__ logits, int ld, int vocab,
                                                                      float* __restrict__ part_val, int* __restrict__ part_idx) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sval[kSampleThreads];
   __shared__ int sidx[kSampleThreads];
   const int row = blockIdx.y, part = blockIdx.x;
@@ -215,6 +219,8 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_part_kernel(const float
 }
 
 __global__ void argmax_pick_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x;       // one warp, kArgmaxParts == 32
   float v = part_val[row * kArgmaxParts + lane];
   int i = part_idx[row * kArgmaxParts + lane];
@@ -234,10 +240,10 @@ ARLE_API int arle_argmax(const float* logits, int ld, int rows, int vocab, float
   if (rows > 65535) return ARLE_E_UNSUPPORTED;
   float* pv = scratch;
   int* pi = reinterpret_cast<int*>(scratch + (size_t)rows * kArgmaxParts);
-  argmax_part_kernel<<<dim3(kArgmaxParts, rows), kSampleThreads, 0, s>>>(logits, ld, vocab, pv, pi);
+  launch_kernel(argmax_part_kernel, dim3(dim3(kArgmaxParts, rows)), dim3(kSampleThreads), 0, s, 1, logits, ld, vocab, pv, pi);
   int rc = launch_status();
   if (rc) return rc;
-  argmax_pick_kernel<<<rows, 32, 0, s>>>(pv, pi, out);
+  launch_kernel(argmax_pick_kernel, dim3(rows), dim3(32), 0, s, 1, pv, pi, out);
   return launch_status();
 }
 
@@ -247,7 +253,7 @@ ARLE_API int arle_sample(const float* logits, int ld, int rows, int vocab, const
   if (rows <= 0) return 0;
   if (vocab <= 0 || ld < vocab) return ARLE_E_BADARG;
   if (temperature && (!uniform || !scratch)) return ARLE_E_BADARG;
-  sample_kernel<<<rows, kSampleThreads, 0, s>>>(logits, ld, vocab, temperature, top_k, top_p, min_p, uniform,
+  launch_kernel(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, s, 1, logits, ld, vocab, temperature, top_k, top_p, min_p, uniform,
                                                 scratch, out);
   return launch_status();
 }
@@ -311,7 +317,7 @@ ARLE_API int arle_sample_static(const float* logits, int ld, int rows, int vocab
   // Nothing in the scratch has to start at zero: the kernel writes every
   // probability of a row before it reads any, so the last call's leftovers are
   // overwritten, not cleared.
-  sample_kernel<<<rows, kSampleThreads, 0, s>>>(logits, ld, vocab, temperature, top_k, top_p, min_p, uniform,
+  launch_kernel(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, s, 1, logits, ld, vocab, temperature, top_k, top_p, min_p, uniform,
                                                 scratch, out);
   return launch_status();
 }

@@ -91,6 +91,16 @@ def check_errors(device) -> None:
         raise KernelError("a kernel gave up a bounded wait (asynchronous copy did not complete); results are invalid")
 
 
+def set_programmatic_launch(on: bool) -> None:
+    """Programmatic dependent launch (off by default): a kernel may be scheduled, set up
+    its barriers and prefetch weights while the kernel before it finishes, and waits
+    for that kernel only before touching its results."""
+    lib = library()
+    lib.arle_set_programmatic_launch.argtypes = [c_int]
+    lib.arle_set_programmatic_launch.restype = None
+    lib.arle_set_programmatic_launch(1 if on else 0)
+
+
 def _dt(t: torch.Tensor) -> int:
     if t.dtype == torch.float32:
         return 0

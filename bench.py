@@ -101,6 +101,7 @@ def main() -> int:
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="profiling aid: run only the decode steps at --batch, or only the prefill")
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--pdl", action="store_true", help="launch kernels with programmatic dependent launch")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -121,6 +122,8 @@ def main() -> int:
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
+    if args.pdl:
+        ops.set_programmatic_launch(True)
     pk = peaks()
     layers = args.layers or QWEN3_8B["num_hidden_layers"]
     model = random_model(QWEN3_8B, seed=0, dtype="bfloat16", device=dev, num_layers=layers)
