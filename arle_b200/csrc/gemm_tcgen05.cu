@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
   pdl_launch_dependents();
   pdl_wait();
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  constexpr uint32_t kTmemCols = 2 * BN <= 256 ? 256 : 512;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[STAGES];      // producer -> MMA: stage holds its two tiles
@@ -155,7 +156,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
   if (warp == 5) {
-    tmem_alloc(smem_addr(&tmem_base_slot), 2 * BN);        // two accumulator buffers
+    tmem_alloc(smem_addr(&tmem_base_slot), kTmemCols);     // two accumulator buffers (a power of two of columns)
     tmem_relinquish();
   }
   tc_fence_before();
@@ -275,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tcgen05_kernel(const __grid_
   __syncthreads();
   if (warp == 5) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && abort_flag && err) atomicExch(err, 2);
 }
@@ -377,12 +378,16 @@ ARLE_API int arle_gemm_tcgen05(const void* x, int ldx, const void* W, int ldw, v
   if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return ARLE_E_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return ARLE_E_UNSUPPORTED;
   if (M > 65535 * BM) return ARLE_E_UNSUPPORTED;
-  const bool wide = N >= 256;
-  if (out_dtype == 1)
-    return wide ? launch<256, 4, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, err, s)
-                : launch<128, 6, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
-  if (out_dtype == 0)
-    return wide ? launch<256, 4, float>(x, ldx, W, ldw, out, ldo, M, N, K, err, s)
-                : launch<128, 6, float>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
+  // Tile width 256, or 128 for narrow outputs.  (Narrower tiles that fill the last wave of
+  // CTAs better were tried and lost more in per-tile efficiency than they gained.)
+  const int best = N >= 256 ? 256 : 128;
+#define ARLE_TC_CASE(BN_, ST_)                                                                                        \
+  if (best == BN_)                                                                                                    \
+    return out_dtype == 1 ? launch<BN_, ST_, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, err, s)                \
+                          : launch<BN_, ST_, float>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
+  if (out_dtype != 0 && out_dtype != 1) return ARLE_E_BADARG;
+  ARLE_TC_CASE(256, 4)
+  ARLE_TC_CASE(128, 6)
+#undef ARLE_TC_CASE
   return ARLE_E_BADARG;
 }

@@ -7,8 +7,11 @@ CPU path: the first call loads the library (building it when needed) and raises
 if that fails or if a tensor is not on a CUDA device.
 
 Matrix products: the float32 path uses the package's own FFMA kernel
-(``gemm_f32.cu``: true 32-bit, fixed summation order).  The bfloat16 path calls
-cuBLAS through ``torch.mm``, as cklxx/arle calls cuBLASLt for its projections
+(``gemm_f32.cu``: true 32-bit, fixed summation order).  The bfloat16 path has two
+kernels of its own: weight streaming for up to 8 rows (``gemm_skinny.cu``, every
+decode step of up to 8 requests) and tcgen05 / TMA / TMEM for many rows
+(``gemm_tcgen05.cu``, switched on with ``set_tcgen05_min_rows``).  Otherwise it calls
+cuBLAS through ``torch.mm``, as cklxx/arle calls cuBLASLt for all its projections
 (crates/cuda-kernels/csrc/gemm/gemv.cu:298-482).
 """
 from __future__ import annotations
@@ -203,12 +206,27 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         _check(library().arle_gemm_skinny(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out), out.stride(0),
                                           M, N, K, _ptr(error_flag(x.device)), _stream()), "gemm_skinny")
         return
+    if M >= _TCGEN05_MIN_ROWS and tcgen05_gemm_supported(x, w, out):
+        gemm_tcgen05(x, w, out)
+        return
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     elif out.dtype == torch.float32:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
         raise KernelError(f"gemm: output type {out.dtype}")
+
+
+_TCGEN05_MIN_ROWS = 1 << 30
+
+
+def set_tcgen05_min_rows(rows: int) -> None:
+    """bfloat16 products with at least this many rows of x run on the package's tcgen05
+    kernel instead of cuBLAS.  Off by default (a very large value): the kernel reaches
+    85 to 90 % of cuBLAS at 2,048 rows and falls behind it below 512, so cuBLAS stands
+    for these products, as cuBLASLt does in cklxx/arle."""
+    global _TCGEN05_MIN_ROWS
+    _TCGEN05_MIN_ROWS = int(rows)
 
 
 def tcgen05_gemm_supported(x, w, out) -> bool:

@@ -102,6 +102,7 @@ def main() -> int:
                     help="profiling aid: run only the decode steps at --batch, or only the prefill")
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--pdl", action="store_true", help="launch kernels with programmatic dependent launch")
+    ap.add_argument("--tcgen05-gemm", action="store_true", help="products of 128 rows and more through the package's tcgen05 kernel instead of cuBLAS")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -124,6 +125,8 @@ def main() -> int:
     torch.cuda.set_device(dev)
     if args.pdl:
         ops.set_programmatic_launch(True)
+    if args.tcgen05_gemm:
+        ops.set_tcgen05_min_rows(128)
     pk = peaks()
     layers = args.layers or QWEN3_8B["num_hidden_layers"]
     model = random_model(QWEN3_8B, seed=0, dtype="bfloat16", device=dev, num_layers=layers)
