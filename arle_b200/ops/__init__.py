@@ -47,6 +47,8 @@ _SIGNATURES = {
     "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
+    "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I,
+                                        _I, _I, _P, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_skinny": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -311,8 +313,9 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
         raise KernelError("paged_attention: block table rows must be contiguous")
     if batch is not None and fast_attention_supported(q, nq, nkv, hd):
         if batch.max_q_len > 1:
-            paged_attention_prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd,
-                                    page_size, scale, window, batch.max_q_len, skip_single=batch.num_single > 0)
+            prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
+            prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
+                    window, batch.max_q_len, skip_single=batch.num_single > 0)
         if batch.num_single > 0:
             splits = decode_splits(batch.num_rows, nkv, block_table.shape[1] * page_size)
             part_o = part_ml = counters = None
@@ -335,6 +338,26 @@ def fast_attention_supported(q, nq: int, nkv: int, hd: int) -> bool:
     runs on the general kernel."""
     return (q.dtype == torch.bfloat16 and hd in (64, 128) and nq // nkv <= 16 and q.stride(0) % 8 == 0
             and q.data_ptr() % 16 == 0)
+
+
+def tc_attention_supported(q, hd: int, page_size: int) -> bool:
+    """The tcgen05 prefill kernel takes head size 128 and pages of a multiple of 16 tokens."""
+    return hd == 128 and page_size % 16 == 0 and q.dtype == torch.bfloat16
+
+
+def paged_attention_prefill_tc(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
+                               window, max_q_len: int, skip_single: bool = False) -> None:
+    """Flash attention over the paged cache on the tcgen05 tensor cores (TMA-fed, scores
+    and output in tensor memory) for rows with several queries."""
+    R = kv_lens.numel()
+    _i32(q_indptr, "q_indptr"), _i32(kv_lens, "kv_lens"), _i32(block_table, "block_table")
+    if not tc_attention_supported(q, hd, page_size) or q.stride(1) != 1 or not out.is_contiguous():
+        raise KernelError("paged_attention_prefill_tc: needs bfloat16, head size 128, page size a multiple of 16")
+    _check(library().arle_paged_attention_prefill_tc(
+        _ptr(q), q.stride(0), q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(q_indptr),
+        _ptr(kv_lens), _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
+        int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _ptr(error_flag(q.device)), _stream()),
+        "paged_attention_prefill_tc")
 
 
 def decode_splits(rows: int, nkv: int, kv_bound: int) -> int:

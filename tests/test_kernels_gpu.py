@@ -374,6 +374,38 @@ def test_prefill_attention_kernel(nq, nkv, hd, ps, window):
     torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,ps,window", [(2, 1, 16, None), (8, 2, 16, None), (32, 8, 16, None), (4, 4, 32, 70), (3, 1, 64, 129),
+                                               (2, 2, 16, 500)])
+def test_prefill_attention_tcgen05_kernel(nq, nkv, ps, window):
+    hd = 128
+    lens, q_lens = [130, 300, 128, 129, 9, 700, 1000], [130, 2, 128, 3, 1, 333, 1000]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=6)
+    out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_prefill_tc(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, max(q_lens))
+    ops.check_errors(DEV)
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, window)
+    torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+
+
+def test_prefill_attention_tcgen05_sharp_scores_and_stale_rows():
+    """Scores far apart (the lazy rescaling of the accumulator must kick in) and a cache
+    whose unused slots hold huge values (they must not leak through P = 0)."""
+    nq, nkv, hd, ps = 4, 2, 128, 16
+    lens, q_lens = [520, 77], [520, 77]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=7, scale_q=6.0)
+    used = torch.zeros(kc.shape[0], ps, dtype=torch.bool)
+    for r, n in enumerate(lens):
+        for j in range(n):
+            used[int(bt[r, j // ps]), j % ps] = True
+    vc[~used.to(DEV)[:, None, :].expand(-1, nkv, -1)] = 3.0e38
+    out = torch.zeros(q.shape[0], nq * hd, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention_prefill_tc(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), None, max(q_lens))
+    ops.check_errors(DEV)
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, None)
+    assert torch.isfinite(out.float()).all()
+    torch.testing.assert_close(out.float().cpu(), exp, rtol=3e-2, atol=2e-2)
+
+
 def test_prefill_and_decode_kernels_split_a_mixed_step():
     nq, nkv, hd, ps = 8, 2, 128, 16
     lens, q_lens = [100, 40, 7, 300], [1, 40, 1, 11]
