@@ -4,25 +4,27 @@
 // One CTA serves 128 consecutive queries of one request and one query head and walks
 // the visible keys in tiles of 128 (boundaries at multiples of 128 of the absolute key
 // position).  Everything big lives where the tensor cores want it:
-//   shared memory : Q (128 x 128), two stages each of K and V (128 keys x 128), P (128 x 128),
+//   shared memory : Q (128 x 128), two stages each of K, V (128 keys x 128) and P (128 x 128),
 //                   all in the 128-byte swizzled layout that TMA writes and tcgen05.mma reads;
 //   tensor memory : two buffers for the scores S (128 lanes x 128 columns, float32) and one
 //                   for the output accumulator O (128 x 128, float32).
 // Roles by warp:
-//   warp 4, one lane : loader.  TMA tile loads (cp.async.bulk.tensor.2d): Q once from the
-//                      packed projection output, then per tile the keys and values page by
-//                      page (16 keys x 64 elements per box) at the rows the block table names.
+//   warps 4 and 6    : loaders (keys; values).  TMA tile loads (cp.async.bulk.tensor.2d): Q
+//                      once from the packed projection output, then per tile the keys or the
+//                      values page by page (16 keys x 64 elements per box, one box per lane)
+//                      at the rows the block table names.
 //   warp 5, one lane : MMA issuer.  S(j) = Q . K(j)^T (eight tcgen05.mma of K 16, both operands
 //                      K-major) into S buffer j mod 2, one tile ahead of the softmax;
 //                      O += P(j) . V(j) (eight tcgen05.mma, V used as it lies in the cache:
 //                      an MN-major B operand).  tcgen05.commit signals the mbarriers.
 //   warps 0-3        : softmax and epilogue; thread i owns query row i (TMEM lane i), so row
-//                      maxima and sums need no shuffles.  Pass 1 reads S and finds the row
-//                      maximum; O and the running sum are rescaled only when the maximum grew
-//                      by more than 2^8 since the last rescale (the exponentials stay within
-//                      float32 and bfloat16 range); pass 2 reads S again, masks (key <= query
-//                      position, and > position - window), exponentiates, adds up and writes P
-//                      as bfloat16 into shared memory, as cklxx/arle's prefill kernel rounds P
+//                      maxima and sums need no shuffles.  A thread reads its row of S into
+//                      registers, masks (key <= query position, and > position - window)
+//                      and finds the row maximum; O and the running sum are rescaled only
+//                      when the maximum grew by more than 2^8 since the last rescale (the
+//                      exponentials stay within float32 and bfloat16 range); then it
+//                      exponentiates, adds up and writes P as bfloat16 into shared memory
+//                      (two buffers), as cklxx/arle's prefill kernel rounds P
 //                      (crates/cuda-kernels/tools/tilelang/batch_prefill_paged_hd128.py:223-225).
 //                      After the last tile the rows are divided by their sums and stored.
 // Scores, maxima, sums and the accumulator are float32.  Every mbarrier wait is bounded;
@@ -36,7 +38,7 @@ namespace {
 constexpr int HD = 128;
 constexpr int BQ = 128;                      // queries per CTA
 constexpr int BKV = 128;                     // keys per tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
 constexpr uint32_t SUB = 128 * 128;          // bytes of a [128 rows x 64 elements] swizzled sub-tile
 constexpr uint32_t TILE = 2 * SUB;           // 128 x 128 bfloat16
 constexpr float kRescaleStep = 8.0f;         // log2 units the maximum may grow before O is rescaled
@@ -100,9 +102,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   unsigned char* q_s = base;                      // TILE
   unsigned char* k_s = base + TILE;               // 2 x TILE
   unsigned char* v_s = base + 3 * TILE;           // 2 x TILE
-  unsigned char* p_s = base + 5 * TILE;           // TILE
-  __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full,
-      pv_done;
+  unsigned char* p_s = base + 5 * TILE;           // 2 x TILE: P of even and of odd tiles
+  __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
+      pv_done[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -117,8 +119,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       mbar_init(smem_addr(&s_full[i]), 1);
       mbar_init(smem_addr(&s_empty[i]), 4);
     }
-    mbar_init(smem_addr(&p_full), 4);
-    mbar_init(smem_addr(&pv_done), 1);
+    mbar_init(smem_addr(&p_full[0]), 4);
+    mbar_init(smem_addr(&p_full[1]), 4);
+    mbar_init(smem_addr(&pv_done[0]), 1);
+    mbar_init(smem_addr(&pv_done[1]), 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -137,45 +141,44 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   const uint32_t tmem_o = tmem_base + 256;
   const volatile int* aborted = &abort_flag;
 
-  if (warp == 4) {
-    // The whole warp loads: a tile of keys and values is 32 boxes (8 pages x 2 halves of the
-    // head x K and V), one per lane, so that their issue overlaps; lane 0 does the waiting
-    // and arms the barriers.
-    if (lane == 0) {
+  if (warp == 4 || warp == 6) {
+    // Warp 4 loads the keys, warp 6 the values, each at its own pace: a tile is 16 boxes per
+    // operand (8 pages x 2 halves of the head), one per lane, so that their issue overlaps;
+    // lane 0 waits for the stage and arms its barrier.  A key stage frees as soon as S of two
+    // tiles ago is computed, a value stage only after P.V of two tiles ago.
+    const bool keys = warp == 4;
+    if (keys && lane == 0) {
       mbar_expect_tx(smem_addr(&q_full), TILE);
       tma_load_2d(smem_addr(q_s), &map_q, h * HD, t0 + mbeg, smem_addr(&q_full));
       tma_load_2d(smem_addr(q_s + SUB), &map_q, h * HD + 64, t0 + mbeg, smem_addr(&q_full));
     }
     const int* bt = block_table + (size_t)r * bt_stride;
-    const int c = lane >> 2, what = lane & 3;            // page of the tile; 0,1: K halves, 2,3: V halves
+    const int c = (lane >> 1) & 7, half = lane & 1;      // page of the tile, half of the head (lanes 0..15)
+    const CUtensorMap* map = keys ? &map_k : &map_v;
+    unsigned char* tile_s = keys ? k_s : v_s;
     for (int j = 0; j < ntiles; ++j) {
       const int st = j & 1;
       const uint32_t par = (uint32_t)((j >> 1) & 1);
       const int key0 = kb + j * BKV + c * 16;
       int row = -1;
-      if (key0 <= p_last && key0 + 15 >= lo) {
+      if (lane < 16 && key0 <= p_last && key0 + 15 >= lo) {
         const int page = bt[key0 / page_size];
         row = (page * nkv + kvh) * page_size + key0 % page_size;
       }
-      const int n = __popc(__ballot_sync(0xffffffffu, row >= 0)) >> 2;      // pages of this tile
+      const int n = __popc(__ballot_sync(0xffffffffu, row >= 0)) >> 1;      // pages of this tile
+      uint64_t* full = keys ? &k_full[st] : &v_full[st];
       int go = 1;
       if (lane == 0) {
-        if (!mbar_wait_bounded(smem_addr(&k_empty[st]), par ^ 1, aborted) ||
-            !mbar_wait_bounded(smem_addr(&v_empty[st]), par ^ 1, aborted)) {
+        if (!mbar_wait_bounded(smem_addr(keys ? &k_empty[st] : &v_empty[st]), par ^ 1, aborted)) {
           abort_flag = 1;
           go = 0;
         } else {
-          mbar_expect_tx(smem_addr(&k_full[st]), (uint32_t)n * 4096u);
-          mbar_expect_tx(smem_addr(&v_full[st]), (uint32_t)n * 4096u);
+          mbar_expect_tx(smem_addr(full), (uint32_t)n * 4096u);
         }
       }
       go = __shfl_sync(0xffffffffu, go, 0);
       if (!go || *aborted) break;
-      if (row >= 0) {
-        unsigned char* dst = (what < 2 ? k_s : v_s) + st * TILE + (what & 1) * SUB + c * 2048;
-        tma_load_2d(smem_addr(dst), what < 2 ? &map_k : &map_v, (what & 1) * 64, row,
-                    smem_addr(what < 2 ? &k_full[st] : &v_full[st]));
-      }
+      if (row >= 0) tma_load_2d(smem_addr(tile_s + st * TILE + half * SUB + c * 2048), map, half * 64, row, smem_addr(full));
     }
   } else if (warp == 5) {
     if (lane == 0) {
@@ -204,17 +207,17 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
         if (j + 1 < ntiles) ok = issue_s(j + 1);
         if (!ok) break;
         const int st = j & 1;
-        if (!mbar_wait_bounded(smem_addr(&p_full), (uint32_t)(j & 1), aborted)) { ok = false; break; }
+        if (!mbar_wait_bounded(smem_addr(&p_full[st]), (uint32_t)((j >> 1) & 1), aborted)) { ok = false; break; }
         if (!mbar_wait_bounded(smem_addr(&v_full[st]), (uint32_t)((j >> 1) & 1), aborted)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t ad = smem_desc_sw128(smem_addr(p_s + (kk >> 2) * SUB)) + 2 * (kk & 3);
+          const uint64_t ad = smem_desc_sw128(smem_addr(p_s + st * TILE + (kk >> 2) * SUB)) + 2 * (kk & 3);
           const uint64_t bd = smem_desc_mn_sw128(smem_addr(v_s + st * TILE + kk * 2048), SUB);
           umma_bf16(tmem_o, ad, bd, idesc_pv, (j | kk) != 0 ? 1u : 0u);
         }
         umma_commit(smem_addr(&v_empty[st]));
-        umma_commit(smem_addr(&pv_done));
+        umma_commit(smem_addr(&pv_done[st]));
       }
       if (!ok) abort_flag = 1;
     }
@@ -232,27 +235,35 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       bool ready = mbar_wait_bounded(smem_addr(&s_full[buf]), (uint32_t)((j >> 1) & 1), aborted);
       if (__any_sync(0xffffffffu, !ready)) { ok = false; break; }
       tc_fence_after();
-      // pass 1: the row maximum of this tile (raw scores; the scale is positive, so it is
-      // applied to the maximum alone).  Four running maxima keep the chain of dependent
-      // instructions short: a softmax warp has its scheduler to itself.
+      // The whole row of scores comes into registers at once (four loads in flight, one
+      // wait), which frees the S buffer for the tile after next right away.
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_base + lane_addr + (uint32_t)(buf * BKV + c * 32), sv[c]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&s_empty[buf]));
+      // the row maximum (raw scores; the scale is positive, so it is applied to the maximum
+      // alone).  Four running maxima keep the chain of dependent instructions short: a
+      // softmax warp has its scheduler to itself.
       float mx;
       {
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + lane_addr + (uint32_t)(buf * BKV + c * 32), v);
-          tmem_ld_wait();
-          if (full_tile) {
+        if (full_tile) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(v[i]));
-          } else {
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[c][i]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const int kj = k0 + c * 32 + i;
-              m4[i & 3] = fmaxf(m4[i & 3], (kj <= p_row && kj >= lo_row) ? __uint_as_float(v[i]) : -INFINITY);
+              if (!(kj <= p_row && kj >= lo_row)) sv[c][i] = 0xff800000u;      // -inf: masked for good
+              m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sv[c][i]));
             }
-          }
         }
         mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * scale_log2;
       }
@@ -262,51 +273,44 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       if (grow) m_used = m_new;
       const float m_eff = m_used == -INFINITY ? 0.f : m_used;
       l *= f;
-      if (j > 0) {
-        ready = mbar_wait_bounded(smem_addr(&pv_done), (uint32_t)((j - 1) & 1), aborted);
+      // O may be touched, and P buffer j mod 2 overwritten, only after the products that
+      // still use them: P.V of tile j-2 read this P buffer; a rescale of O needs P.V of
+      // tile j-1 complete (which implies tile j-2).  Tile t signals pv_done[t mod 2]; its
+      // completions there are numbered t / 2, so a waiter is never two phases behind.
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, f != 1.0f);
+      if (rescale) {
+        ready = mbar_wait_bounded(smem_addr(&pv_done[(j - 1) & 1]), (uint32_t)(((j - 1) >> 1) & 1), aborted);
         if (__any_sync(0xffffffffu, !ready)) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, f != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
-            tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-            tmem_st32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tmem_st32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
         }
+        tmem_st_wait();
+      } else if (j > 1) {
+        ready = mbar_wait_bounded(smem_addr(&pv_done[j & 1]), (uint32_t)(((j - 2) >> 1) & 1), aborted);
+        if (__any_sync(0xffffffffu, !ready)) { ok = false; break; }
       }
-      // pass 2: exponentials (one fused multiply-add and one ex2 each), their sum in four
-      // partial sums, and P as bfloat16 in the swizzled K-major layout
+      // exponentials (one fused multiply-add and one ex2 each; a masked score is -inf and
+      // gives 0), their sum in four partial sums, and P as bfloat16 in the swizzled
+      // K-major layout
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + lane_addr + (uint32_t)(buf * BKV + c * 32), v);
-        tmem_ld_wait();
         uint32_t packed[16];
-        if (full_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float e0 = ex2_fast(fmaf(__uint_as_float(v[i]), scale_log2, -m_eff));
-            const float e1 = ex2_fast(fmaf(__uint_as_float(v[i + 1]), scale_log2, -m_eff));
-            l4[(i >> 1) & 3] += e0 + e1;
-            packed[i >> 1] = pack_bf16x2(e0, e1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const int kj = k0 + c * 32 + i;
-            const float e0 = (kj <= p_row && kj >= lo_row) ? ex2_fast(fmaf(__uint_as_float(v[i]), scale_log2, -m_eff)) : 0.f;
-            const float e1 = (kj + 1 <= p_row && kj + 1 >= lo_row) ? ex2_fast(fmaf(__uint_as_float(v[i + 1]), scale_log2, -m_eff)) : 0.f;
-            l4[(i >> 1) & 3] += e0 + e1;
-            packed[i >> 1] = pack_bf16x2(e0, e1);
-          }
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = ex2_fast(fmaf(__uint_as_float(sv[c][i]), scale_log2, -m_eff));
+          const float e1 = ex2_fast(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, -m_eff));
+          l4[(i >> 1) & 3] += e0 + e1;
+          packed[i >> 1] = pack_bf16x2(e0, e1);
         }
-        unsigned char* prow = p_s + (c >> 1) * SUB + row * 128;
+        unsigned char* prow = p_s + buf * TILE + (c >> 1) * SUB + row * 128;
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const int chunk = ((c & 1) * 4 + q4) ^ (row & 7);
@@ -318,13 +322,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       tc_fence_before();
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(smem_addr(&s_empty[buf]));
-        mbar_arrive(smem_addr(&p_full));
-      }
+      if (lane == 0) mbar_arrive(smem_addr(&p_full[buf]));
     }
     if (ok) {
-      const bool ready = mbar_wait_bounded(smem_addr(&pv_done), (uint32_t)((ntiles - 1) & 1), aborted);
+      const bool ready = mbar_wait_bounded(smem_addr(&pv_done[(ntiles - 1) & 1]), (uint32_t)(((ntiles - 1) >> 1) & 1), aborted);
       if (__any_sync(0xffffffffu, !ready)) ok = false;
     }
     if (ok) {
@@ -384,7 +385,7 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
   if (rc) return rc;
   rc = tensor_map_2d_bf16(v_cache, cache_rows, HD, HD, 16, &mv);
   if (rc) return rc;
-  const size_t smem = 6 * (size_t)TILE + 1024;
+  const size_t smem = 7 * (size_t)TILE + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
