@@ -1,4 +1,7 @@
 // Token embedding: residual[t, :] = float32(table[ids[t], :]).
+// A negative id is a placeholder for "the token this request sampled last": it is read
+// from last_token[slot_of_token[t]], which the sampling kernels write on the device, so
+// that a decode step can be launched before the host has seen the previous step's tokens.
 // The residual stream is kept in 32-bit in both engine precisions, so the table
 // row is widened here once.  An id outside [0, vocab) writes zeros and raises the
 // error flag instead of reading out of bounds (the host checks ids first).
@@ -8,11 +11,13 @@ using namespace arle;
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab,
-                                 int* __restrict__ err) {
+                                 int* __restrict__ err, const int* __restrict__ last_token,
+                                 const int* __restrict__ slot_of_token) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  if (id < 0 && last_token) id = last_token[slot_of_token[t]];
   float* o = out + (size_t)t * hidden;
   if (id < 0 || id >= vocab) {
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
@@ -25,11 +30,13 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 
 // Eight table elements per thread and step (16-byte loads of bfloat16 rows).
 __global__ void embedding_bf16_vec_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
-                                          float* __restrict__ out, int hidden, int vocab, int* __restrict__ err) {
+                                          float* __restrict__ out, int hidden, int vocab, int* __restrict__ err,
+                                          const int* __restrict__ last_token, const int* __restrict__ slot_of_token) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  if (id < 0 && last_token) id = last_token[slot_of_token[t]];
   const bool bad = id < 0 || id >= vocab;
   if (bad && threadIdx.x == 0 && err) atomicExch(err, 1);
   const uint4* row = reinterpret_cast<const uint4*>(table + (size_t)(bad ? 0 : id) * hidden);
@@ -44,20 +51,22 @@ __global__ void embedding_bf16_vec_kernel(const int* __restrict__ ids, const __n
 }
 
 ARLE_API int arle_embedding(const int* ids, const void* table, int table_dtype, float* out,
-                            int num_tokens, int hidden, int vocab, int* err, cudaStream_t s) {
+                            int num_tokens, int hidden, int vocab, int* err, const int* last_token,
+                            const int* slot_of_token, cudaStream_t s) {
+  if (last_token && !slot_of_token) return ARLE_E_BADARG;
   if (num_tokens <= 0) return 0;
   if (hidden <= 0 || vocab <= 0) return ARLE_E_BADARG;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == 1 && hidden % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     int th = hidden / 8;
     th = th <= 32 ? 32 : (th <= 64 ? 64 : (th <= 128 ? 128 : (th <= 256 ? 256 : 512)));
-    launch_kernel(embedding_bf16_vec_kernel, dim3(num_tokens), dim3(th), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err);
+    launch_kernel(embedding_bf16_vec_kernel, dim3(num_tokens), dim3(th), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err, last_token, slot_of_token);
     return launch_status();
   }
   if (table_dtype == 0)
-    launch_kernel(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const float*)table, out, hidden, vocab, err);
+    launch_kernel(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const float*)table, out, hidden, vocab, err, last_token, slot_of_token);
   else if (table_dtype == 1)
-    launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err);
+    launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, s, 1, ids, (const __nv_bfloat16*)table, out, hidden, vocab, err, last_token, slot_of_token);
   else
     return ARLE_E_BADARG;
   return launch_status();

@@ -218,7 +218,8 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_part_kernel(const float
   }
 }
 
-__global__ void argmax_pick_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int* __restrict__ out) {
+__global__ void argmax_pick_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int* __restrict__ out,
+                                   const int* __restrict__ scatter, int* __restrict__ last_token) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x, lane = threadIdx.x;       // one warp, kArgmaxParts == 32
@@ -230,11 +231,18 @@ __global__ void argmax_pick_kernel(const float* __restrict__ part_val, const int
     const int oi = __shfl_xor_sync(0xffffffffu, i, o);
     if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
   }
-  if (lane == 0) out[row] = i == 0x7fffffff ? 0 : i;
+  if (lane == 0) {
+    const int tok = i == 0x7fffffff ? 0 : i;
+    out[row] = tok;
+    if (scatter) last_token[scatter[row]] = tok;
+  }
 }
 
 // All rows greedy.  scratch: float32 [rows * 64] (values in the first half, indices in the second).
-ARLE_API int arle_argmax(const float* logits, int ld, int rows, int vocab, float* scratch, int* out, cudaStream_t s) {
+// scatter / last_token (may both be null): last_token[scatter[row]] = the row's token, for the
+// placeholder ids of the embedding kernel.
+ARLE_API int arle_argmax(const float* logits, int ld, int rows, int vocab, float* scratch, int* out, const int* scatter,
+                         int* last_token, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (vocab <= 0 || ld < vocab || !scratch) return ARLE_E_BADARG;
   if (rows > 65535) return ARLE_E_UNSUPPORTED;
@@ -243,7 +251,22 @@ ARLE_API int arle_argmax(const float* logits, int ld, int rows, int vocab, float
   launch_kernel(argmax_part_kernel, dim3(dim3(kArgmaxParts, rows)), dim3(kSampleThreads), 0, s, 1, logits, ld, vocab, pv, pi);
   int rc = launch_status();
   if (rc) return rc;
-  launch_kernel(argmax_pick_kernel, dim3(rows), dim3(32), 0, s, 1, pv, pi, out);
+  launch_kernel(argmax_pick_kernel, dim3(rows), dim3(32), 0, s, 1, pv, pi, out, scatter, last_token);
+  return launch_status();
+}
+
+__global__ void scatter_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ scatter,
+                                      int* __restrict__ last_token, int rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < rows) last_token[scatter[r]] = tokens[r];
+}
+
+ARLE_API int arle_scatter_tokens(const int* tokens, const int* scatter, int* last_token, int rows, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (!tokens || !scatter || !last_token) return ARLE_E_BADARG;
+  launch_kernel(scatter_tokens_kernel, dim3((rows + 127) / 128), dim3(128), 0, s, 1, tokens, scatter, last_token, rows);
   return launch_status();
 }
 

@@ -74,9 +74,11 @@ class GroupTables:
 class StepContext:
     """Device-side description of one step, handed to every part.
 
-    token_ids, positions, row_of_token: int32 [T].  q_indptr: int32 [R+1] (row r
-    owns token rows q_indptr[r] .. q_indptr[r+1]-1).  kv_lens: int32 [R], tokens the
-    request holds after this step.  state_slots: int32 [R].  want_rows: int32 [W].
+    token_ids, positions, row_of_token, slot_of_token: int32 [T] (a negative token id
+    stands for the token its request sampled last, kept on the device in ``last_token``).
+    q_indptr: int32 [R+1] (row r owns token rows q_indptr[r] .. q_indptr[r+1]-1).
+    kv_lens: int32 [R], tokens the request holds after this step.  state_slots: int32 [R].
+    want_rows, want_slots: int32 [W] (token row and request slot of each wanted place).
     Host-side copies of what launch shapes depend on: q_lens, kv_lens_host,
     max_q_len, max_kv_len, decode_only."""
 
@@ -97,6 +99,9 @@ class StepContext:
         self.table_width = 0
         self.token_ids = self.positions = self.row_of_token = None
         self.q_indptr = self.kv_lens = self.state_slots = self.want_rows = None
+        self.slot_of_token = self.want_slots = None
+        self.last_token: Optional[torch.Tensor] = None       # int32 [slots]: each request's last sampled token
+        self.h2d_bytes = 0
         self.groups: List[GroupTables] = []
         self._pinned: Optional[torch.Tensor] = None
         self._dev: Optional[torch.Tensor] = None
@@ -130,7 +135,7 @@ class StepContext:
             widths.append(table_width if table_width is not None else need)
         self.table_width = max(widths) if widths else 0
         # layout of the packed int32 array
-        sizes = [T, T, T, R + 1, R, R, max(W, 1)]
+        sizes = [T, T, T, R + 1, R, R, max(W, 1), T, max(W, 1)]
         for gi in range(n_groups):
             sizes += [R * widths[gi], T]
         offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])
@@ -144,34 +149,59 @@ class StepContext:
         kvl = h[offs[4]:offs[4] + R]
         sts = h[offs[5]:offs[5] + R]
         want = h[offs[6]:offs[6] + W]
-        at = 0
-        wi = 0
-        qi[0] = 0
-        for r, (e, st, n) in enumerate(zip(entries, starts, q_lens)):
-            tok[at:at + n] = np.asarray(e.tokens, dtype=np.int32)
-            pos[at:at + n] = np.arange(st, st + n, dtype=np.int32)
-            row[at:at + n] = r
-            for w in e.want:
-                if not 0 <= w < n:
-                    raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")
-                want[wi] = at + w
-                wi += 1
-            at += n
-            qi[r + 1] = at
-            kvl[r] = st + n
-            sts[r] = cm.slot(e.request)
-        for gi in range(n_groups):
-            bt = h[offs[7 + 2 * gi]:offs[7 + 2 * gi] + R * widths[gi]].reshape(R, widths[gi])
-            bt[:] = cm.block_rows(gi, self.requests, widths[gi])
-            sm = h[offs[8 + 2 * gi]:offs[8 + 2 * gi] + T]
+        slot_tok = h[offs[7]:offs[7] + T]
+        want_slot = h[offs[8]:offs[8] + W]
+        slots = np.fromiter((cm.slot(e.request) for e in entries), dtype=np.int64, count=R)
+        starts_np = np.asarray(starts, dtype=np.int64)
+        sts[:] = slots
+        if self.max_q_len == 1 and W == R and all(tuple(e.want) == (0,) for e in entries):
+            # every entry is one decoded token whose logits are wanted: no loops over requests
+            tok[:] = [e.tokens[0] for e in entries]
+            pos[:] = starts_np
+            row[:] = np.arange(R)
+            qi[:] = np.arange(R + 1)
+            kvl[:] = starts_np + 1
+            want[:] = np.arange(R)
+            slot_tok[:] = slots
+            want_slot[:] = slots
+            for gi, g in enumerate(cm.groups):
+                bt = h[offs[9 + 2 * gi]:offs[9 + 2 * gi] + R * widths[gi]].reshape(R, widths[gi])
+                bt[:] = g.table[slots, :widths[gi]]
+                pages = g.table[slots, starts_np // g.page_size].astype(np.int64)
+                if (pages < 0).any():
+                    raise RuntimeError(f"a token of this step has no page in cache group {gi}")
+                h[offs[10 + 2 * gi]:offs[10 + 2 * gi] + T] = pages * g.page_size + starts_np % g.page_size
+        else:
             at = 0
-            for e, st, n in zip(entries, starts, q_lens):
-                sm[at:at + n] = cm.slot_mapping(gi, e.request, st, n)
+            wi = 0
+            qi[0] = 0
+            for r, (e, st, n) in enumerate(zip(entries, starts, q_lens)):
+                tok[at:at + n] = np.asarray(e.tokens, dtype=np.int32)
+                pos[at:at + n] = np.arange(st, st + n, dtype=np.int32)
+                row[at:at + n] = r
+                slot_tok[at:at + n] = slots[r]
+                for w in e.want:
+                    if not 0 <= w < n:
+                        raise ValueError(f"request {e.request!r}: wanted place {w} is not among its {n} tokens")
+                    want[wi] = at + w
+                    want_slot[wi] = slots[r]
+                    wi += 1
                 at += n
+                qi[r + 1] = at
+                kvl[r] = st + n
+            for gi in range(n_groups):
+                bt = h[offs[9 + 2 * gi]:offs[9 + 2 * gi] + R * widths[gi]].reshape(R, widths[gi])
+                bt[:] = cm.block_rows(gi, self.requests, widths[gi])
+                sm = h[offs[10 + 2 * gi]:offs[10 + 2 * gi] + T]
+                at = 0
+                for e, st, n in zip(entries, starts, q_lens):
+                    sm[at:at + n] = cm.slot_mapping(gi, e.request, st, n)
+                    at += n
         dev = self._device_buffer(total)
         dev[:total].copy_(host[:total], non_blocking=True)
         if self._copied is not None:
             self._copied.record()
+        self.h2d_bytes = total * 4
         d = dev
         self.token_ids = d[offs[0]:offs[0] + T]
         self.positions = d[offs[1]:offs[1] + T]
@@ -180,10 +210,12 @@ class StepContext:
         self.kv_lens = d[offs[4]:offs[4] + R]
         self.state_slots = d[offs[5]:offs[5] + R]
         self.want_rows = d[offs[6]:offs[6] + W]
+        self.slot_of_token = d[offs[7]:offs[7] + T]
+        self.want_slots = d[offs[8]:offs[8] + W]
         self.groups = []
         for gi in range(n_groups):
-            bt = d[offs[7 + 2 * gi]:offs[7 + 2 * gi] + R * widths[gi]].view(R, widths[gi])
-            sm = d[offs[8 + 2 * gi]:offs[8 + 2 * gi] + T]
+            bt = d[offs[9 + 2 * gi]:offs[9 + 2 * gi] + R * widths[gi]].view(R, widths[gi])
+            sm = d[offs[10 + 2 * gi]:offs[10 + 2 * gi] + T]
             self.groups.append(GroupTables(bt, sm))
         return self
 

@@ -65,13 +65,14 @@ class Engine:
         per_page = self._bytes_per_page(model, o.page_size, dtype)
         pages = o.num_pages if o.num_pages is not None else self._pages_from_memory(per_page, o, max_seq)
         self.runner = ModelRunner(model, o.page_size, pages, o.num_slots, max_seq, o.device)
-        if o.cuda_graph and hasattr(self.runner, "enable_graphs"):
+        if o.cuda_graph and torch.device(o.device).type == "cuda":
             self.runner.enable_graphs()
         self.scheduler = Scheduler(self.runner.cache, SchedulerConfig(
             o.max_num_batched_tokens, o.chunked_prefill_size, o.max_prefill_tokens, o.prefill_max_requests,
             o.scheduler_mixed_policy), model.spec.stop_token_ids, o.max_tokens)
         self.sampler = Sampler(model.spec.vocab_size, o.device)
         self._rngs: Dict[object, object] = {}
+        self._inflight: list = []           # (plan, sample handle) of the steps launched in the last tick
         self._next_id = 0
 
     @staticmethod
@@ -106,20 +107,41 @@ class Engine:
         return req
 
     def step(self) -> list:
-        """One scheduler tick (one or two model steps).  Returns the requests that
-        finished in it."""
-        finished = []
-        for plan in self.scheduler.schedule():
+        """One scheduler tick (one or two model steps).  The tick's steps are launched
+        first, with the tokens of the previous tick still on their way (the device hands
+        each request's last token to its next step itself); then the previous tick's
+        tokens are read and booked.  Returns the requests that finished by them."""
+        plans = self.scheduler.schedule()
+        if any(e.count > 1 and -1 in e.tokens for p in plans for e in p.entries):
+            finished = self._drain()            # a prompt portion must know all its tokens
+        else:
+            finished = None
+        launched = []
+        for plan in plans:
             entries = [StepEntry(e.request.rid, e.tokens, (e.count - 1,) if e.samples else ()) for e in plan.entries]
             sampling = [e.request for e in plan.entries if e.samples]
             logits = self.runner.step(entries)
-            sampled = []
+            handle = None
             if sampling:
-                sampled = self.sampler.sample(logits, [r.params for r in sampling], [self._rngs[r.rid] for r in sampling])
-            done = self.scheduler.on_step_done(plan, sampled)
+                handle = self.sampler.sample_async(logits, [r.params for r in sampling],
+                                                   [self._rngs[r.rid] for r in sampling],
+                                                   self.runner.last_ctx.want_slots, self.runner.last_token)
+            self.scheduler.on_launch(plan)
+            launched.append((plan, handle))
+        if finished is None:
+            finished = self._drain()
+        self._inflight = launched
+        return finished
+
+    def _drain(self) -> list:
+        """Reads the tokens of the steps in flight and books them."""
+        finished = []
+        for plan, handle in self._inflight:
+            done = self.scheduler.on_step_done(plan, handle.result() if handle is not None else [])
             for r in done:
                 self._rngs.pop(r.rid, None)
             finished.extend(done)
+        self._inflight = []
         return finished
 
     def generate(self, prompts: Sequence[Sequence[int]],
@@ -134,14 +156,18 @@ class Engine:
         reqs = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
         seen = {r.rid: 0 for r in reqs}
         while any(r.finish_reason is None for r in reqs):
-            if not self.scheduler.has_work():
+            if self.scheduler.has_work():
+                self.step()
+            elif self._inflight:
+                self._drain()
+            else:
                 raise RuntimeError("scheduler has no work but requests are unfinished")
-            self.step()
             if on_token is not None:
                 for r in reqs:
-                    for t in r.output[seen[r.rid]:]:
-                        on_token(r.rid, t)
-                    seen[r.rid] = len(r.output)
+                    while seen[r.rid] < len(r.output) and r.output[seen[r.rid]] >= 0:
+                        on_token(r.rid, r.output[seen[r.rid]])
+                        seen[r.rid] += 1
+        self._drain()
         self.scheduler.finished.clear()
         if torch.device(self.options.device).type == "cuda":
             from .. import ops

@@ -31,6 +31,11 @@ class ModelRunner:
                                   max_tokens_per_request or model.spec.max_position, model.dtype, self.device)
         self.ws = Workspace(self.device)
         self.ctx = StepContext(self.cache, self.ws)
+        # the token each request sampled last, written by the sampling kernels; a step entry
+        # whose single token id is negative reads its token from here
+        self.last_token = torch.zeros(max_slots, dtype=torch.int32, device=self.device)
+        self.ctx.last_token = self.last_token
+        self.last_ctx = self.ctx
         self.steps_run = 0
         self.tokens_run = 0
         self.graph_steps = 0
@@ -86,6 +91,8 @@ class ModelRunner:
         for e in entries:
             if not self.cache.has_request(e.request):
                 self.cache.add_request(e.request)
+            if len(e.tokens) == 1 and int(e.tokens[0]) < 0:
+                continue                            # the token this request sampled last, still on the device
             for t in e.tokens:
                 if not 0 <= int(t) < vocab:
                     raise ValueError(f"request {e.request!r}: token id {t} is outside the vocabulary [0, {vocab})")
@@ -107,6 +114,7 @@ class ModelRunner:
             self.cache.release_passed(e.request)
         self.steps_run += 1
         self.tokens_run += ctx.num_tokens
+        self.last_ctx = ctx
         return logits
 
 
@@ -120,6 +128,7 @@ class _DecodeGraph:
         self.table_width = table_width
         self.ws = Workspace(runner.device)
         self.ctx = StepContext(runner.cache, self.ws)
+        self.ctx.last_token = runner.last_token
         self.graph = None
         self.logits = None
         self.launches = 0

@@ -28,6 +28,12 @@ Policies, and where cklxx/arle has the same:
   its generated tokens and recomputes them as part of its prompt, so its output
   is unchanged.  A lone request that cannot grow is finished with reason
   "length".
+* A step may be launched before the tokens of the step before it are known on the host:
+  ``on_launch`` appends a placeholder (-1) for every token that step will sample, so the
+  next ``schedule`` can plan the following decode rows (whose token the device hands over
+  itself), and ``on_step_done`` fills the placeholders in when the tokens arrive.  cklxx/arle
+  overlaps launch and readback the same way (scheduler/cuda/execution.rs:677-709).  A stop
+  token is therefore seen one step late: the extra step's token is dropped.
 * Finish: a sampled stop token (the model's and the request's, unless
   ``ignore_eos``) ends the request with "stop" and is not emitted
   (decode.rs:785-791); ``max_new_tokens`` generated, or the most tokens a request
@@ -72,6 +78,8 @@ class Request:
     num_computed: int = 0
     finish_reason: Optional[str] = None
     preemptions: int = 0
+    unresolved: Deque[int] = field(default_factory=deque)   # places in ``tokens`` whose sampled token is still on its way
+    closed: bool = False                                     # its last token has been launched; it is not scheduled again
 
     @property
     def remaining(self) -> int:
@@ -96,6 +104,7 @@ class PlannedEntry:
 @dataclass
 class StepPlan:
     entries: List[PlannedEntry]
+    launched: bool = False
 
     @property
     def num_tokens(self) -> int:
@@ -168,11 +177,15 @@ class Scheduler:
         self.waiting.appendleft(req)
 
     def _finish(self, req: Request, reason: str) -> None:
+        if req.finish_reason is not None:
+            return
         req.finish_reason = reason
         if self.cache.has_request(req.rid):
             self.cache.free_request(req.rid)
         if req in self.running:
             self.running.remove(req)
+        if req in self.waiting:
+            self.waiting.remove(req)
         self.finished.append(req)
         self.stats["finished"] += 1
 
@@ -271,12 +284,15 @@ class Scheduler:
         return [StepPlan(rows + portions)]
 
     # ---------------------------------------------------------------- results
-    def on_step_done(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
-        """``sampled``: one token per entry of the plan that ``samples``, in order.
-        Returns the requests that finished."""
-        done = []
-        it = iter(sampled)
+    def on_launch(self, plan: StepPlan) -> None:
+        """The plan's step has been handed to the device.  Its tokens count as computed,
+        and every token it will sample is entered as a placeholder (-1) to be filled in by
+        ``on_step_done``.  A request whose last token this is (``max_new_tokens``, or the
+        most tokens a request may hold) leaves the running set and gives its cache back
+        now: whatever is launched later runs after this step on the device."""
+        plan.launched = True
         self.stats["steps"] += 1
+        limit = self.max_request_tokens()
         for e in plan.entries:
             r = e.request
             r.num_computed += e.count
@@ -286,15 +302,44 @@ class Scheduler:
                 self.stats["prefill_tokens"] += e.count
             if not e.samples:
                 continue
+            r.unresolved.append(len(r.tokens))
+            r.tokens.append(-1)
+            r.output.append(-1)
+            if len(r.output) >= r.max_new_tokens or len(r.tokens) >= limit:
+                r.closed = True
+                if r in self.running:
+                    self.running.remove(r)
+                if self.cache.has_request(r.rid):
+                    self.cache.free_request(r.rid)
+
+    def on_step_done(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """``sampled``: one token per entry of the plan that ``samples``, in order.
+        Returns the requests that finished."""
+        if not plan.launched:
+            self.on_launch(plan)
+        done = []
+        it = iter(sampled)
+        for e in plan.entries:
+            if not e.samples:
+                continue
             tok = int(next(it))
+            r = e.request
+            if r.finish_reason == "stop" or not r.unresolved:
+                continue                                    # a token sampled past a stop token: dropped
+            at = r.unresolved.popleft()
             stops = self.stop_ids | set(r.params.stop_token_ids)
             if not r.params.ignore_eos and tok in stops:
+                del r.tokens[at:]                           # the stop token is not emitted, nor anything after it
+                del r.output[at - len(r.prompt):]
+                r.unresolved.clear()
                 self._finish(r, "stop")
                 done.append(r)
                 continue
-            r.tokens.append(tok)
-            r.output.append(tok)
-            if len(r.output) >= r.max_new_tokens or len(r.tokens) >= self.max_request_tokens():
+            r.tokens[at] = tok
+            r.output[at - len(r.prompt)] = tok
+            if r.closed and not r.unresolved:
+                was_open = r.finish_reason is None
                 self._finish(r, "length")
-                done.append(r)
+                if was_open:
+                    done.append(r)
         return done

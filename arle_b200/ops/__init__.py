@@ -39,7 +39,7 @@ def add_launches(n: int) -> None:
 
 _P, _I, _F = c_void_p, c_int, c_float
 _SIGNATURES = {
-    "arle_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+    "arle_embedding": [_P, _P, _I, _P, _I, _I, _I, _P, _P, _P, _P],
     "arle_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "arle_residual_add": [_P, _P, _I, _I, _I, _P],
     "arle_silu_mul": [_P, _P, _I, _I, _I, _P],
@@ -52,7 +52,8 @@ _SIGNATURES = {
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_skinny": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
-    "arle_argmax": [_P, _I, _I, _I, _P, _P, _P],
+    "arle_argmax": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
+    "arle_scatter_tokens": [_P, _P, _P, _I, _P],
     "arle_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
 }
 
@@ -145,16 +146,24 @@ def _i32(t, name):
 
 
 # ------------------------------------------------------------------- embedding
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor = None) -> None:
-    """out[t, :] = float32(table[ids[t], :]).  ids int32 [T]; out float32 [T, H]."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor = None,
+              last_token: torch.Tensor = None, slot_of_token: torch.Tensor = None) -> None:
+    """out[t, :] = float32(table[ids[t], :]).  ids int32 [T]; out float32 [T, H].  With
+    ``last_token`` (int32, one entry per request slot) and ``slot_of_token`` (int32 [T]) a
+    negative id stands for last_token[slot_of_token[t]], the token the request sampled last."""
     T, H = out.shape
     if out.dtype != torch.float32 or not out.is_contiguous() or not table.is_contiguous():
         raise KernelError("embedding: out must be contiguous float32 and the table contiguous")
     if ids.numel() != T or table.shape[1] != H:
         raise KernelError(f"embedding: shapes ids {tuple(ids.shape)} table {tuple(table.shape)} out {tuple(out.shape)}")
     _i32(ids, "ids")
+    if last_token is not None:
+        _i32(last_token, "last_token"), _i32(slot_of_token, "slot_of_token")
+        if slot_of_token is None or slot_of_token.numel() != T:
+            raise KernelError("embedding: slot_of_token must name a slot for every token")
     _check(library().arle_embedding(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, table.shape[0],
-                                    _ptr(err), _stream()), "embedding")
+                                    _ptr(err), _ptr(last_token), _ptr(slot_of_token) if last_token is not None else None,
+                                    _stream()), "embedding")
 
 
 # ------------------------------------------------------------------------ norm
@@ -412,16 +421,29 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 
 # -------------------------------------------------------------------- sampling
-def argmax(logits, scratch, out) -> None:
+def argmax(logits, scratch, out, scatter=None, last_token=None) -> None:
     """out[r] = index of the largest logit of row r (ties: the lowest index), float32
-    logits [R, V]; scratch float32 [R * 64]."""
+    logits [R, V]; scratch float32 [R * 64].  With ``scatter`` (int32 [R]) and ``last_token``
+    the token also goes to last_token[scatter[r]] (see ``embedding``)."""
     R, V = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32 or out.numel() < R:
         raise KernelError("argmax: float32 logits with unit inner stride, int32 out with one entry per row")
     if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < R * 64:
         raise KernelError("argmax: scratch must be float32 with 64 entries per row")
-    _check(library().arle_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(scratch), _ptr(out), _stream()), "argmax")
+    if (scatter is None) != (last_token is None) or (scatter is not None and scatter.numel() < R):
+        raise KernelError("argmax: scatter and last_token go together, one scatter entry per row")
+    _check(library().arle_argmax(_ptr(logits), logits.stride(0), R, V, _ptr(scratch), _ptr(out), _ptr(_i32(scatter, "scatter")),
+                                 _ptr(_i32(last_token, "last_token")), _stream()), "argmax")
     add_launches(1)
+
+
+def scatter_tokens(tokens, scatter, last_token) -> None:
+    """last_token[scatter[r]] = tokens[r] (all int32), for tokens chosen by ``sample``."""
+    R = scatter.numel()
+    _i32(tokens, "tokens"), _i32(scatter, "scatter"), _i32(last_token, "last_token")
+    if tokens.numel() < R:
+        raise KernelError("scatter_tokens: one token per scatter entry")
+    _check(library().arle_scatter_tokens(_ptr(tokens), _ptr(scatter), _ptr(last_token), R, _stream()), "scatter_tokens")
 
 
 def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out) -> None:

@@ -130,7 +130,8 @@ class DecoderModel:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         T, H = ctx.num_tokens, self.spec.hidden_size
         resid = ctx.ws.get("residual", (T, H), torch.float32)
-        ops.embedding(ctx.token_ids, self.embed, resid)
+        ops.embedding(ctx.token_ids, self.embed, resid, None, getattr(ctx, "last_token", None),
+                      getattr(ctx, "slot_of_token", None))
         stream = ResidualStream(resid, ctx.ws, self.dtype)
         for i, e in enumerate(self.spec.schedule):
             cl = self.entry_cache_layer[i]

@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import Sampler, request_rng
+from .sampler import SampleHandle, Sampler, request_rng
 
-__all__ = ["SamplingParams", "Sampler", "request_rng"]
+__all__ = ["SamplingParams", "SampleHandle", "Sampler", "request_rng"]

@@ -17,8 +17,11 @@ import torch
 F32 = torch.float32
 
 
-def embedding(ids, table, out, err=None):
-    out.copy_(table[ids.long()].to(F32))
+def embedding(ids, table, out, err=None, last_token=None, slot_of_token=None):
+    ids = ids.long()
+    if last_token is not None:
+        ids = torch.where(ids < 0, last_token[slot_of_token.long()].long(), ids)
+    out.copy_(table[ids].to(F32))
 
 
 def rmsnorm(resid, delta, rows, weight, eps, out, write_resid):
@@ -94,8 +97,14 @@ def silu_mul(gate_up, out):
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
 
-def argmax(logits, scratch, out):
+def argmax(logits, scratch, out, scatter=None, last_token=None):
     out[: logits.shape[0]] = torch.argmax(logits, dim=1).to(out.dtype)      # torch returns the first maximal index
+    if scatter is not None:
+        last_token[scatter[: logits.shape[0]].long()] = out[: logits.shape[0]]
+
+
+def scatter_tokens(tokens, scatter, last_token):
+    last_token[scatter.long()] = tokens[: scatter.numel()]
 
 
 def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out):
@@ -129,4 +138,4 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out):
         out[r] = int(hit[0]) if hit.numel() else int(torch.nonzero(p > 0)[-1])
 
 
-ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "attention_prep", "paged_attention", "silu_mul", "argmax", "sample")
+ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "attention_prep", "paged_attention", "silu_mul", "argmax", "scatter_tokens", "sample")
