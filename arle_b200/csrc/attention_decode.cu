@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
     int bt_stride, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nq, int nkv,
-    int page_size, float scale_log2, int window, int splits) {
+    int page_size, int ps_shift, float scale_log2, int window, int splits) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int ROW = HD + 8;                 // padded row, in elements: 16 B more keeps ldmatrix conflict-free
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
   };
   auto load_tile = [&](int tile, int stage) {
     const int k0 = beg + tile * kTile;
-    const int first = k0 / page_size;
+    const int first = ps_shift >= 0 ? (k0 >> ps_shift) : k0 / page_size;
     const int* pg = pgbuf[tile & 3];
     __nv_bfloat16* kd = ks + stage * kTile * ROW;
     __nv_bfloat16* vd = vs + stage * kTile * ROW;
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(kThreads) paged_decode_kernel(
       const bool ok = kj < end;
       size_t off = 0;
       if (ok) {
-        const int pidx = kj / page_size;
+        const int pidx = ps_shift >= 0 ? (kj >> ps_shift) : kj / page_size;     // pages are mostly a power of two
         off = (size_t)pg[pidx - first] * page_stride + (size_t)(kj - pidx * page_size) * HD + part * 8;
       }
       cp_async16(smem_u32(kd + key * ROW + part * 8), kbase + off, ok ? 16 : 0);
@@ -305,6 +305,9 @@ int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cach
                   float* part_ml, int* counters, int nq, int nkv, int page_size, float scale, int window, int rows,
                   int splits, cudaStream_t s) {
   constexpr int ROW = HD + 8;
+  int ps_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (ps_shift = 0; (1 << ps_shift) < page_size; ++ps_shift) {}
   const size_t tiles = (size_t)(4 * kTile + 16) * ROW * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)(4 * 16 * HD + 128) * sizeof(float);
   const size_t smem = tiles > merge ? tiles : merge;
@@ -318,7 +321,7 @@ int launch_decode(const void* q, int q_row_stride, void* out, const void* k_cach
   launch_kernel(paged_decode_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 1, 
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters, nq, nkv,
-      page_size, scale * 1.4426950408889634f, window, splits);
+      page_size, ps_shift, scale * 1.4426950408889634f, window, splits);
   return launch_status();
 }
 

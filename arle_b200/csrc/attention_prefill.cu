@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table,
-    int bt_stride, int nq, int nkv, int page_size, float scale_log2, int window, int skip_single) {
+    int bt_stride, int nq, int nkv, int page_size, int ps_shift, float scale_log2, int window, int skip_single) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int ROW = HD + 8;
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
   };
   auto load_tile = [&](int tile, int stage) {
     const int k0 = kb + tile * kTile;
-    const int first = max(lo, k0) / page_size;
+    const int first = ps_shift >= 0 ? (max(lo, k0) >> ps_shift) : max(lo, k0) / page_size;
     const int* pg = pgbuf[tile & 3];
     __nv_bfloat16* kd = ks + stage * kTile * ROW;
     __nv_bfloat16* vd = vs + stage * kTile * ROW;
@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(kThreads, 3) paged_prefill_kernel(
       const bool ok = kj >= lo && kj <= p_last;
       size_t off = 0;
       if (ok) {
-        const int pidx = kj / page_size;
+        const int pidx = ps_shift >= 0 ? (kj >> ps_shift) : kj / page_size;     // pages are mostly a power of two
         off = (size_t)pg[pidx - first] * page_stride + (size_t)(kj - pidx * page_size) * HD + part * 8;
       }
       cp_async16(smem_u32(kd + key * ROW + part * 8), kbase + off, ok ? 16 : 0);
@@ -240,6 +240,9 @@ int launch_prefill(const void* q, int q_row_stride, void* out, const void* k_cac
                    const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, int nq, int nkv,
                    int page_size, float scale, int window, int rows, int max_q_len, int skip_single, cudaStream_t s) {
   constexpr int ROW = HD + 8;
+  int ps_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (ps_shift = 0; (1 << ps_shift) < page_size; ++ps_shift) {}
   const size_t smem = (size_t)(4 * kTile) * ROW * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
@@ -250,7 +253,7 @@ int launch_prefill(const void* q, int q_row_stride, void* out, const void* k_cac
   dim3 grid((max_q_len + kBlockM - 1) / kBlockM, nq, rows);
   launch_kernel(paged_prefill_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 1, 
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
-      (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, nq, nkv, page_size,
+      (const __nv_bfloat16*)v_cache, q_indptr, kv_lens, block_table, bt_stride, nq, nkv, page_size, ps_shift,
       scale * 1.4426950408889634f, window, skip_single);
   return launch_status();
 }

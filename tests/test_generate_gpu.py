@@ -136,6 +136,24 @@ def test_long_decoding(models):
     assert len(o.token_ids) == 300
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_long_decoding_bf16_fast_kernels(name, tmp_path):
+    """300 decoded tokens in bfloat16 on the configurations whose sizes reach the tensor-core
+    attention and weight-streaming kernels: every emitted token must be (within bfloat16
+    rounding) the plain model's best at its place, so a fault that builds up along the
+    sequence (a page's edge, a split boundary) shows as a token the plain model rates low."""
+    d = make_model_dir(name, seed=23, root=str(tmp_path))
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    prompt = torch.randint(6, cfg["vocab_size"], (37,), generator=torch.Generator().manual_seed(5)).tolist()
+    eng = Engine(d, dtype="bfloat16", page_size=16, num_pages=40, num_slots=2)
+    o = eng.generate([prompt], SamplingParams(max_new_tokens=300, ignore_eos=True))[0]
+    toks = prompt + o.token_ids
+    lg = plain.forward(w, cfg, toks[:-1])
+    gaps = [float(lg[i].max() - lg[i][toks[i + 1]]) for i in range(len(prompt) - 1, len(toks) - 1)]
+    assert len(o.token_ids) == 300 and max(gaps) < 0.06 and sum(g == 0 for g in gaps) > 0.9 * len(gaps)
+    assert eng.runner.graph_steps > 250
+
+
 def test_command_line_run_json(models):
     d, cfg, w, prompts = models["A"]
     r = subprocess.run([sys.executable, "-m", "arle_b200", "--model-path", d, "--max-tokens", "6", "--dtype", "float32",
