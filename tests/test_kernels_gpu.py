@@ -226,8 +226,9 @@ def test_paged_attention_finds_a_far_key():
 @pytest.mark.parametrize("nq,nkv,hd,ps,rot,norm", [(4, 2, 16, 4, 16, True), (6, 1, 32, 8, 32, True),
                                                     (3, 3, 48, 16, 48, True), (8, 2, 128, 16, 128, True),
                                                     (2, 1, 64, 16, 32, False), (2, 2, 256, 8, 0, True)])
-def test_attention_prep(dtype, nq, nkv, hd, ps, rot, norm):
-    T, pages = 23, 9
+@pytest.mark.parametrize("T", [23, 70])
+def test_attention_prep(dtype, nq, nkv, hd, ps, rot, norm, T):
+    pages = -(-T // ps) + 6
     width = (nq + 2 * nkv) * hd
     qkv = rnd(T, width, dtype=dtype, scale=2.0, seed=1)
     pos = torch.randint(0, 5000, (T,), dtype=torch.int32, device=DEV)
