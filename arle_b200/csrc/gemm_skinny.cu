@@ -37,6 +37,7 @@ constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
 constexpr int kXPad = 8;                     // elements of padding per x row (16 bytes): rows fall on different banks
 constexpr int kRowPad = 16;                  // bytes of padding per weight-row segment of a stage
+constexpr int kPartTiles = 16;                // tiles whose partial sums a CTA of a cluster keeps for one reduction at the end
 constexpr uint32_t kSpinLimit = 1u << 22;    // polls of an mbarrier before giving up (a few hundred ms)
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -82,8 +83,8 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
   off += (size_t)kWarps * SLOTS * STAGE;
   float* red = reinterpret_cast<float*>(smem_raw + off);                                     // [2][kWarps][16][NT*8]
   off += (size_t)2 * kWarps * 16 * NT * 8 * sizeof(float);
-  float* part = reinterpret_cast<float*>(smem_raw + off);                                    // [2][16][NT*8] (clusters)
-  off += (size_t)2 * 16 * NT * 8 * sizeof(float);
+  float* part = reinterpret_cast<float*>(smem_raw + off);                                    // [kPartTiles][16][NT*8] (clusters)
+  off += (size_t)kPartTiles * 16 * NT * 8 * sizeof(float);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + off);                              // [kWarps][SLOTS], then x's
   uint64_t* xbar = bars + kWarps * SLOTS;
 
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
   const int tiles = (r1 - r0 + 15) / 16;
   const int spt = (klen + KB - 1) / KB;                   // stages per 16-row tile
   const int total = tiles * spt;
+  const bool batched = csize > 1 && tiles <= kPartTiles;    // few tiles: one cluster reduction at the end
 
   if (lane == 0) {
     for (int s = 0; s < SLOTS; ++s) mbar_init(smem_u32(&bars[warp * SLOTS + s]), 1);
@@ -162,9 +164,13 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
 
   int done = 0;                                             // stages of this warp consumed so far
   for (int tile = 0; tile < tiles; ++tile) {
-    float acc[NT][4];
+    // two accumulator sets, used by alternate K steps, halve the chain of dependent MMAs
+    float acc[NT][4], acc2[NT][4];
 #pragma unroll
-    for (int n = 0; n < NT; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    for (int n = 0; n < NT; ++n) {
+      acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+      acc2[n][0] = acc2[n][1] = acc2[n][2] = acc2[n][3] = 0.f;
+    }
     for (;;) {
       const int s = warp + done * kWarps;
       if (s >= total || s / spt != tile) break;
@@ -177,15 +183,19 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       const uint32_t st = smem_u32(stages + (size_t)(warp * SLOTS + slot) * STAGE);
       const uint32_t a_addr = st + (lane & 15) * PITCH + (lane >> 4) * 16;
       const __nv_bfloat16* xb = xs + (size_t)g * xrow + kloc + 2 * tq;
-#pragma unroll 4
-      for (int kk = 0; kk < len; kk += 16) {
-        uint32_t a[4];
+#pragma unroll 2
+      for (int kk = 0; kk < len; kk += 32) {          // len is a multiple of 32
+        uint32_t a[4], a2[4];
         ldsm_x4(a_addr + kk * 2, a[0], a[1], a[2], a[3]);
+        ldsm_x4(a_addr + kk * 2 + 32, a2[0], a2[1], a2[2], a2[3]);
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
           const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xb + (size_t)n * 8 * xrow + kk);
           const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xb + (size_t)n * 8 * xrow + kk + 8);
+          const uint32_t b2 = *reinterpret_cast<const uint32_t*>(xb + (size_t)n * 8 * xrow + kk + 16);
+          const uint32_t b3 = *reinterpret_cast<const uint32_t*>(xb + (size_t)n * 8 * xrow + kk + 24);
           mma_bf16(acc[n], a, b0, b1);
+          mma_bf16(acc2[n], a2, b2, b3);
         }
       }
       __syncwarp();
@@ -201,10 +211,10 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
     float* rw = red + ((size_t)(tile & 1) * kWarps + warp) * 16 * NT * 8;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
-      rw[g * NT * 8 + n * 8 + 2 * tq] = acc[n][0];
-      rw[g * NT * 8 + n * 8 + 2 * tq + 1] = acc[n][1];
-      rw[(g + 8) * NT * 8 + n * 8 + 2 * tq] = acc[n][2];
-      rw[(g + 8) * NT * 8 + n * 8 + 2 * tq + 1] = acc[n][3];
+      rw[g * NT * 8 + n * 8 + 2 * tq] = acc[n][0] + acc2[n][0];
+      rw[g * NT * 8 + n * 8 + 2 * tq + 1] = acc[n][1] + acc2[n][1];
+      rw[(g + 8) * NT * 8 + n * 8 + 2 * tq] = acc[n][2] + acc2[n][2];
+      rw[(g + 8) * NT * 8 + n * 8 + 2 * tq + 1] = acc[n][3] + acc2[n][3];
     }
     __syncthreads();
     const int rt = r0 + tile * 16;
@@ -217,10 +227,11 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       if (csize == 1) {
         if (m < M && rt + row < r1) store_out<OutT>(out + (size_t)m * ldo + rt + row, s);
       } else {
-        part[(tile & 1) * 16 * NT * 8 + tid] = s;
+        part[(batched ? tile : (tile & 1)) * 16 * NT * 8 + tid] = s;
       }
     }
-    if (csize > 1) {
+    if (csize > 1 && !batched) {
+      // too many tiles to keep: rank 0 adds the ranks' sums tile by tile
       cg::cluster_group cluster = cg::this_cluster();
       cluster.sync();
       if (rank == 0 && tid < 16 * NT * 8) {
@@ -234,7 +245,24 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       }
     }
   }
-  if (csize > 1) cg::this_cluster().sync();                 // no CTA leaves while its partial sums may still be read
+  if (csize > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (batched && rank == 0 && tid < 16 * NT * 8) {
+      // one reduction for all tiles: rank 0 adds the ranks' sums, in rank order
+      const int row = tid & 15, m = tid >> 4;
+      for (int tile = 0; tile < tiles; ++tile) {
+        float s = 0.f;
+        for (int rk = 0; rk < csize; ++rk) {
+          const float* remote = cluster.map_shared_rank(part, rk);
+          s += remote[tile * 16 * NT * 8 + tid];
+        }
+        const int rt = r0 + tile * 16;
+        if (m < M && rt + row < r1) store_out<OutT>(out + (size_t)m * ldo + rt + row, s);
+      }
+    }
+    if (batched) cluster.sync();                            // no CTA leaves while its partial sums may still be read
+  }
   if (timed_out && err) atomicExch(err, 1);
 }
 
@@ -243,7 +271,7 @@ size_t smem_bytes(int KS) {
   size_t n = ((size_t)NT * 8 * (KS + kXPad) * 2 + 127) / 128 * 128;
   n += (size_t)kWarps * SLOTS * 16 * (KB * 2 + kRowPad);
   n += (size_t)2 * kWarps * 16 * NT * 8 * sizeof(float);
-  n += (size_t)2 * 16 * NT * 8 * sizeof(float);
+  n += (size_t)kPartTiles * 16 * NT * 8 * sizeof(float);
   n += (size_t)(kWarps * SLOTS + 1) * sizeof(uint64_t);
   return n;
 }
