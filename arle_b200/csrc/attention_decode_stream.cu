@@ -1,0 +1,507 @@
+// Streaming paged attention for decoded tokens (one query per request), bfloat16, head
+// sizes 64 and 128, up to 16 query heads per kv head, page sizes that are multiples of 16.
+//
+// Decoding reads every key and value of the batch once; the kernel is built so that this
+// stream never stops.  A grid of one CTA per SM stays resident.  The work is cut into units
+// of one 64-key tile of one (request, kv head) pair, ordered by request, kv head and key
+// position, and every CTA takes the same number of consecutive units whatever the lengths
+// of the requests are; a CTA's range may end in the middle of one pair and go on into the
+// next.  Roles by warp:
+//   warp 8, producer : walks the CTA's units and brings each tile's keys and values in with
+//                      TMA (cp.async.bulk.tensor.3d, boxes of 16 keys of the whole head at the
+//                      rows the block table names, 128-byte swizzle) into a ring of stages,
+//                      as far ahead as the ring is deep; it never waits for arithmetic.
+//   warps 0-7        : two groups of four warps take tiles in turn.  A warp owns 16 keys of
+//                      its group's tile: Q.K^T and P.V on the tensor cores (mma.sync
+//                      m16n8k16, the query heads of the kv head padded to 16 rows), scores,
+//                      online softmax and accumulators in float32, P rounded to bfloat16 for
+//                      P.V as in cklxx/arle's decode kernel
+//                      (crates/cuda-kernels/tools/tilelang/batch_decode_paged_hd128.py:134-231).
+// When a pair's units end (or the CTA's range does) the eight warps merge their partial
+// results in shared memory.  A pair that one CTA covered alone is written out; otherwise the
+// CTA stores an unnormalised partial (o, m, l) and the CTA that arrives last at the pair's
+// counter combines the pieces in the order of the keys (the reference's split-KV variant
+// runs a second kernel for that, :239-463).  Nothing waits for another CTA.
+// Rows whose step entry has more than one token are skipped.  The key range of a row is
+// [max(0, kv_len - window), kv_len).  Every mbarrier wait is bounded: when one runs out the
+// kernel raises the error flag, stops waiting and runs to its end.
+#include "common.cuh"
+#include "mma_utils.cuh"
+#include "tcgen05_utils.cuh"
+using namespace arle;
+
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 32;
+constexpr int kTile = 64;                          // keys per unit
+constexpr int kMaxStages = 8;
+
+__device__ __forceinline__ void mbar_arrive_one(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumers) : "memory"); }
+
+// Where a CTA's range of units meets the rows: which row, kv head and tile a unit is.
+struct Rows {
+  const int* prefix;     // [R + 1] units before each row
+  const int* kvl;        // [R] keys of the row, -1 for a row that is not decoded here
+  int R, nkv, window;
+  __device__ __forceinline__ void tiles_of(int r, int& lo, int& kv_len, int& tlo, int& thi) const {
+    kv_len = kvl[r];
+    lo = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    tlo = lo / kTile;
+    thi = (kv_len + kTile - 1) / kTile;
+  }
+  // the row r with prefix[r] <= u < prefix[r + 1]
+  __device__ __forceinline__ int row_of(int u) const {
+    int a = 0, b = R;                   // invariant: prefix[a] <= u < prefix[b]
+    while (b - a > 1) {
+      const int mid = (a + b) >> 1;
+      if (prefix[mid] <= u) a = mid; else b = mid;
+    }
+    return a;
+  }
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+    const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
+    const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride,
+    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int R, int nq, int nkv,
+    int bt_width, int page_size, int ps_shift, float scale_log2, int window, int stages, int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr uint32_t OPERAND = kTile * HD * 2;            // bytes of the keys (or the values) of one stage
+  constexpr uint32_t STAGE = 2 * OPERAND;
+  constexpr uint32_t BOX = 16 * HD * 2;                   // bytes of one box: 16 keys, as HD / 64 blocks of [16 x 128 bytes]
+  constexpr int NBOX = 2 * 4;                             // boxes of a stage: keys and values, 4 x 16 keys each
+  const int G = nq / nkv;
+  const int C = (int)gridDim.x;
+
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* ring = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  float* mo = reinterpret_cast<float*>(ring + (size_t)stages * STAGE);      // [8][G][HD] partial outputs of the warps
+  float* mm = mo + kConsumerWarps * G * HD;                                 // [8][16] maxima
+  float* mlv = mm + kConsumerWarps * 16;                                    // [8][16] sums
+  int* prefix = reinterpret_cast<int*>(mlv + kConsumerWarps * 16);          // [R + 1]
+  int* kvl = prefix + R + 1;                                                // [R]
+  int* tok = kvl + R;                                                       // [R]
+  __shared__ __align__(8) uint64_t full[kMaxStages], empty[kMaxStages];
+  __shared__ int abort_flag, is_last;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int i = 0; i < stages; ++i) {
+      mbar_init(smem_addr(&full[i]), 1);
+      mbar_init(smem_addr(&empty[i]), 4);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  // A warp reads a 16-key block of a stage only if the block has a key in range, and such a
+  // block was loaded whole (slots of its page beyond the last key hold old, finite cache
+  // contents that meet P = 0), so the ring needs no clearing.
+  if (warp == kConsumerWarps && lane < 2) {
+    const CUtensorMap* m = lane ? &map_v : &map_k;
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(m) : "memory");
+  }
+  for (int r = tid; r < R; r += kThreads) {
+    const int t = q_indptr[r];
+    const bool single = q_indptr[r + 1] - t == 1;
+    const int kv_len = single ? kv_lens[r] : -1;
+    kvl[r] = kv_len;
+    tok[r] = t;
+    int units = 0;
+    if (kv_len > 0) {
+      const int lo = (window > 0 && kv_len > window) ? kv_len - window : 0;
+      units = ((kv_len + kTile - 1) / kTile - lo / kTile) * nkv;
+    }
+    prefix[r + 1] = units;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    if (lane == 0) prefix[0] = 0;
+    for (int base = 0; base < R; base += 32) {
+      const int i = base + lane;
+      int v = i < R ? prefix[i + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      if (i < R) prefix[i + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+
+  const int U = prefix[R];
+  const int per = max(1, (U + C - 1) / C);               // units per CTA
+  const int u0 = (int)blockIdx.x * per;
+  const int u1 = min(U, u0 + per);
+  if (u0 >= u1) return;
+  const Rows rows{prefix, kvl, R, nkv, window};
+  const volatile int* aborted = &abort_flag;
+  const uint32_t ring_addr = smem_addr(ring);
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------------------------ producer
+    const int op = lane >> 2;                             // 0 keys, 1 values
+    const int c = lane & 3;                               // 16-key block of the tile
+    const CUtensorMap* map = op ? &map_v : &map_k;
+    const uint32_t dst_off = (uint32_t)op * OPERAND + (uint32_t)c * BOX;
+    int st = 0, issued = 0;
+    uint32_t par = 0;
+    bool ok = true;
+    for (int u = u0; u < u1 && ok;) {
+      const int r = rows.row_of(u);
+      int lo, kv_len, tlo, thi;
+      rows.tiles_of(r, lo, kv_len, tlo, thi);
+      const int T = thi - tlo;
+      const int rem = u - prefix[r];
+      const int kvh = rem / T;
+      const int tile0 = tlo + rem % T;
+      const int pe = min(prefix[r] + (kvh + 1) * T, u1);
+      const int ntile = pe - u;
+      const int* bt = block_table + (size_t)r * bt_stride;
+      auto wanted = [&](int key0) { return lane < NBOX && key0 < kv_len && key0 + 16 > lo; };
+      auto page_index = [&](int key) { return ps_shift >= 0 ? key >> ps_shift : key / page_size; };
+      // Page ids come 32 at a time, one per lane, and a second 32 ahead of them, so that no
+      // tile waits for a read of the block table; a lane picks its page with a shuffle.
+      int p0 = page_index(tile0 * kTile);
+      int cur = __ldg(bt + min(p0 + lane, bt_width - 1));
+      int nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
+      int key0 = tile0 * kTile + c * 16;
+      for (int i = 0; i < ntile; ++i) {
+        while (page_index(key0 - c * 16) - p0 >= 32) {
+          cur = nxt;
+          p0 += 32;
+          nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
+        }
+        const bool active = wanted(key0);
+        const int pi = page_index(key0);
+        const int rel = pi - p0;                       // 0 .. 63
+        const int from_cur = __shfl_sync(0xffffffffu, cur, rel & 31), from_nxt = __shfl_sync(0xffffffffu, nxt, rel & 31);
+        const int page = rel < 32 ? from_cur : from_nxt;
+        const int row = (page * nkv + kvh) * page_size + (key0 - pi * page_size);
+        const int nb = __popc(__ballot_sync(0xffffffffu, active));
+        int go = 1;
+        if (lane == 0) {
+          if (!mbar_wait_bounded(smem_addr(&empty[st]), par ^ 1, aborted)) {
+            abort_flag = 1;
+            go = 0;
+          } else {
+            mbar_expect_tx(smem_addr(&full[st]), (uint32_t)nb * BOX);
+          }
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) {
+          ok = false;
+          break;
+        }
+        if (active) tma_load_3d(ring_addr + (uint32_t)st * STAGE + dst_off, map, 0, row, 0, smem_addr(&full[st]));
+        ++issued;
+        key0 += kTile;
+        if (++st == stages) st = 0, par ^= 1;
+      }
+      u = pe;
+    }
+    // after a wait ran out: let the copies that are still in flight land before the CTA ends
+    if (*aborted && lane == 0) {
+      for (int s = 0; s < stages && s < issued; ++s) {
+        const int last = (issued - 1 - s) / stages * stages + s;       // last tile issued into stage s
+        mbar_wait_plain(smem_addr(&full[s]), (uint32_t)((last / stages) & 1));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    const int grp = warp >> 2, wk = warp & 3;
+    const int g = lane >> 2, tq = lane & 3;
+    const uint32_t sw = (uint32_t)(lane & 7);
+    int st = 0, n = 0;
+    uint32_t par = 0;
+    for (int u = u0; u < u1;) {
+      const int r = rows.row_of(u);
+      int lo, kv_len, tlo, thi;
+      rows.tiles_of(r, lo, kv_len, tlo, thi);
+      const int T = thi - tlo;
+      const int rem = u - prefix[r];
+      const int kvh = rem / T;
+      const int tile0 = tlo + rem % T;
+      const int pair_begin = prefix[r] + kvh * T;
+      const int pe = min(pair_begin + T, u1);
+      const int ntile = pe - u;
+      const int t = tok[r];
+
+      // the G query heads of this kv head as the A operand: rows 0..G-1 of 16, the rest zero
+      uint32_t qa[HD / 16][4];
+      {
+        const uint32_t* q0 = reinterpret_cast<const uint32_t*>(q + (size_t)t * q_row_stride + (size_t)(kvh * G + g) * HD) + tq;
+        const uint32_t* q1 = q0 + 8 * HD / 2;
+#pragma unroll
+        for (int s = 0; s < HD / 16; ++s) {
+          qa[s][0] = g < G ? __ldg(q0 + s * 8) : 0u;
+          qa[s][1] = g + 8 < G ? __ldg(q1 + s * 8) : 0u;
+          qa[s][2] = g < G ? __ldg(q0 + s * 8 + 4) : 0u;
+          qa[s][3] = g + 8 < G ? __ldg(q1 + s * 8 + 4) : 0u;
+        }
+      }
+      float o[HD / 8][4];
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+      float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8
+
+      for (int i = 0; i < ntile; ++i, ++n) {
+        const int my_st = st;
+        const uint32_t my_par = par;
+        if (++st == stages) st = 0, par ^= 1;
+        if ((n & 1) != grp) continue;
+        if (!mbar_wait_bounded(smem_addr(&full[my_st]), my_par, aborted)) abort_flag = 1;
+        const int kbeg = (tile0 + i) * kTile + wk * 16;        // this warp's 16 keys
+        if (kbeg < kv_len && kbeg + 16 > lo) {
+          const uint32_t kt = ring_addr + (uint32_t)my_st * STAGE + (uint32_t)wk * BOX;
+          const uint32_t vt = kt + OPERAND;
+          // two accumulator sets, one for the even and one for the odd 16-element steps of the
+          // head: half as long a chain of dependent tensor-core instructions
+          float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+          float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t j = (uint32_t)(kk * 2 + ((lane >> 3) & 1));
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(kt + (j >> 3) * (16 * 128) + (uint32_t)((lane >> 4) * 8 + (lane & 7)) * 128 + (((j & 7) ^ sw) << 4), b0, b1,
+                    b2, b3);
+            if (kk & 1) {
+              mma_bf16(s2[0], qa[kk], b0, b1);
+              mma_bf16(s2[1], qa[kk], b2, b3);
+            } else {
+              mma_bf16(s[0], qa[kk], b0, b1);
+              mma_bf16(s[1], qa[kk], b2, b3);
+            }
+          }
+#pragma unroll
+          for (int nn = 0; nn < 2; ++nn)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nn][e] += s2[nn][e];
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+          for (int nn = 0; nn < 2; ++nn) {
+            const int kj = kbeg + 8 * nn + 2 * tq;
+            const bool in0 = kj < kv_len && kj >= lo, in1 = kj + 1 < kv_len && kj + 1 >= lo;
+            s[nn][0] = in0 ? s[nn][0] * scale_log2 : -INFINITY;
+            s[nn][1] = in1 ? s[nn][1] * scale_log2 : -INFINITY;
+            s[nn][2] = in0 ? s[nn][2] * scale_log2 : -INFINITY;
+            s[nn][3] = in1 ? s[nn][3] * scale_log2 : -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[nn][0], s[nn][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[nn][2], s[nn][3]));
+          }
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+          const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);   // finite: the block has a key in range
+          const float c0 = exp2f(m0 - mn0), c1 = exp2f(m1 - mn1);
+          m0 = mn0;
+          m1 = mn1;
+          float p[2][4];
+#pragma unroll
+          for (int nn = 0; nn < 2; ++nn) {
+            p[nn][0] = exp2f(s[nn][0] - mn0);
+            p[nn][1] = exp2f(s[nn][1] - mn0);
+            p[nn][2] = exp2f(s[nn][2] - mn1);
+            p[nn][3] = exp2f(s[nn][3] - mn1);
+          }
+          l0 = l0 * c0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
+          l1 = l1 * c1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
+          uint32_t pa[4];
+          pa[0] = pack_bf16(p[0][0], p[0][1]);
+          pa[1] = pack_bf16(p[0][2], p[0][3]);
+          pa[2] = pack_bf16(p[1][0], p[1][1]);
+          pa[3] = pack_bf16(p[1][2], p[1][3]);
+          // the accumulator is rescaled only when some row's maximum grew (a factor of exactly 1 otherwise)
+          const bool rescale = __any_sync(0xffffffffu, c0 != 1.0f || c1 != 1.0f);
+          if (rescale) {
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+              o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
+            }
+          }
+#pragma unroll
+          for (int dn = 0; dn < HD / 16; ++dn) {
+            const uint32_t j = (uint32_t)(dn * 2 + (lane >> 4));
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_t(vt + (j >> 3) * (16 * 128) + (uint32_t)(((lane >> 3) & 1) * 8 + (lane & 7)) * 128 + (((j & 7) ^ sw) << 4),
+                      b0, b1, b2, b3);
+            mma_bf16(o[2 * dn], pa, b0, b1);
+            mma_bf16(o[2 * dn + 1], pa, b2, b3);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive_one(smem_addr(&empty[my_st]));
+      }
+
+      // ---- merge the eight warps' partial results of this piece
+      l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+      l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        if (g < G) *reinterpret_cast<float2*>(mo + (warp * G + g) * HD + i * 8 + 2 * tq) = make_float2(o[i][0], o[i][1]);
+        if (g + 8 < G) *reinterpret_cast<float2*>(mo + (warp * G + g + 8) * HD + i * 8 + 2 * tq) = make_float2(o[i][2], o[i][3]);
+      }
+      if (tq == 0) {
+        mm[warp * 16 + g] = m0;
+        mm[warp * 16 + g + 8] = m1;
+        mlv[warp * 16 + g] = l0;
+        mlv[warp * 16 + g + 8] = l1;
+      }
+      consumer_sync();
+      const int pidx = r * nkv + kvh;
+      const int first_cta = pair_begin / per, last_cta = (pair_begin + T - 1) / per;
+      const int pieces = last_cta - first_cta + 1;
+      const int slot = (int)blockIdx.x + pidx;                // pieces of a pair lie side by side: first_cta + pidx ...
+      for (int i = tid; i < G * HD; i += kConsumers) {
+        const int row = i / HD, d = i % HD;
+        float M = mm[row];
+#pragma unroll
+        for (int w = 1; w < kConsumerWarps; ++w) M = fmaxf(M, mm[w * 16 + row]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+          const float f = exp2f(mm[w * 16 + row] - M);        // a warp without keys has m = -inf: factor 0
+          L += mlv[w * 16 + row] * f;
+          O += mo[(w * G + row) * HD + d] * f;
+        }
+        if (pieces == 1) {
+          out[((size_t)t * nq + kvh * G + row) * HD + d] = __float2bfloat16_rn(O / L);
+        } else {
+          part_o[((size_t)slot * G + row) * HD + d] = O;
+          if (d == 0) {
+            part_ml[((size_t)slot * G + row) * 2] = M;
+            part_ml[((size_t)slot * G + row) * 2 + 1] = L;
+          }
+        }
+      }
+      if (pieces > 1) {
+        // The piece that arrives last combines all of them:
+        //   out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),  M = max_s m_s,
+        // accumulated piece by piece in the order of the keys.
+        __threadfence();
+        consumer_sync();
+        if (tid == 0) {
+          const int prev = atomicAdd(&counters[pidx], 1);
+          is_last = prev == pieces - 1;
+          if (is_last) counters[pidx] = 0;                    // ready for the next launch
+        }
+        consumer_sync();
+        if (is_last) {
+          __threadfence();
+          const size_t base = (size_t)(first_cta + pidx) * G;
+          for (int i = tid; i < G * HD / 2; i += kConsumers) {
+            const int row = i / (HD / 2), d = (i % (HD / 2)) * 2;
+            const float2* po = reinterpret_cast<const float2*>(part_o + (base + row) * HD + d);
+            const float2* pml = reinterpret_cast<const float2*>(part_ml) + base + row;
+            float M = -INFINITY, L = 0.f, O0 = 0.f, O1 = 0.f;
+            for (int sp0 = 0; sp0 < pieces; sp0 += 8) {        // eight pieces' loads in flight together
+              float2 ml[8], ov[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const int sp = min(sp0 + k, pieces - 1);
+                ml[k] = __ldcg(pml + (size_t)sp * G);
+                ov[k] = __ldcg(po + (size_t)sp * G * HD / 2);
+              }
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                if (sp0 + k < pieces && ml[k].y > 0.f) {
+                  const float Mn = fmaxf(M, ml[k].x);
+                  const float c = exp2f(M - Mn), f = exp2f(ml[k].x - Mn);
+                  L = L * c + ml[k].y * f;
+                  O0 = O0 * c + ov[k].x * f;
+                  O1 = O1 * c + ov[k].y * f;
+                  M = Mn;
+                }
+              }
+            }
+            const float inv = 1.0f / L;
+            *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)t * nq + kvh * G + row) * HD + d) = __floats2bfloat162_rn(O0 * inv, O1 * inv);
+          }
+        }
+      }
+      consumer_sync();                                        // the scratch is free for the next piece
+      u = pe;
+    }
+  }
+  if (*aborted && lane == 0 && err) atomicExch(err, 4);
+}
+
+size_t fixed_smem(int G, int hd, int ctas, int R) {
+  size_t n = (size_t)kConsumerWarps * G * hd * 4 + (size_t)kConsumerWarps * 16 * 2 * 4 + 64;
+  n += (size_t)(3 * R + 1) * 4;
+  return (n + 15) / 16 * 16;
+}
+
+template <int HD>
+int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_row_stride, void* out,
+                  const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, float* part_o,
+                  float* part_ml, int* counters, int rows, int nq, int nkv, int bt_width, int page_size, float scale, int window,
+                  int ctas, int* err, cudaStream_t s) {
+  int ps_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (ps_shift = 0; (1 << ps_shift) < page_size; ++ps_shift) {}
+  int dev = 0, max_smem = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  const size_t stage = (size_t)2 * kTile * HD * 2;
+  const size_t fixed = fixed_smem(nq / nkv, HD, ctas, rows) + 1024 + 256;      // alignment slack, static shared memory
+  if (fixed + 3 * stage > (size_t)max_smem) return ARLE_E_UNSUPPORTED;
+  int stages = (int)(((size_t)max_smem - fixed) / stage);
+  if (stages > kMaxStages) stages = kMaxStages;
+  const size_t smem = fixed - 256 + (size_t)stages * stage;
+  e = cudaFuncSetAttribute(decode_stream_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - 256);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_kernel(decode_stream_kernel<HD>, dim3(ctas), dim3(kThreads), smem, s, 1, mk, mv, (const __nv_bfloat16*)q,
+                    q_row_stride, (__nv_bfloat16*)out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
+                    rows, nq, nkv, bt_width, page_size, ps_shift, scale * 1.4426950408889634f, window, stages, err);
+  if (e != cudaSuccess) return (int)e;
+  return launch_status();
+}
+
+}  // namespace
+
+// k_cache / v_cache: [cache_pages, nkv, page_size, hd].  Scratch: part_o float32
+// [(ctas + rows * nkv) * (nq / nkv) * hd], part_ml float32 [(ctas + rows * nkv) * (nq / nkv) * 2], counters
+// int32 [rows * nkv] that must be zero before the first launch (the kernel leaves them zero).
+// ctas: CTAs of the grid (the number of SMs).  bt_width: columns of the block table, which bound
+// a row's keys.  err: set to 4 if a bounded wait ran out.
+ARLE_API int arle_paged_attention_decode_stream(const void* q, int q_row_stride, void* out, const void* k_cache,
+                                                const void* v_cache, long long cache_pages, const int* q_indptr,
+                                                const int* kv_lens, const int* block_table, int bt_stride, int bt_width,
+                                                float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
+                                                int page_size, float scale, int window, int rows, int ctas, int* err,
+                                                cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || page_size <= 0 || page_size % 16 != 0) return ARLE_E_UNSUPPORTED;
+  if (ctas < 1 || ctas > 1024 || rows > 2048 || !part_o || !part_ml || !counters) return ARLE_E_BADARG;
+  if ((q_row_stride % 2) != 0 || ((uintptr_t)q & 3) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return ARLE_E_UNSUPPORTED;
+  // units are counted in 32 bits
+  const long long max_units = (long long)rows * nkv * (((long long)bt_width * page_size + kTile - 1) / kTile + 1);
+  if (max_units >= (1ll << 30)) return ARLE_E_UNSUPPORTED;
+  if (hd != 64 && hd != 128) return ARLE_E_UNSUPPORTED;
+  CUtensorMap mk, mv;
+  const long long cache_rows = cache_pages * nkv * page_size;
+  int rc = tensor_map_rows_bf16(k_cache, cache_rows, hd, &mk);
+  if (rc) return rc;
+  rc = tensor_map_rows_bf16(v_cache, cache_rows, hd, &mv);
+  if (rc) return rc;
+  if (hd == 128)
+    return launch_stream<128>(mk, mv, q, q_row_stride, out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
+                              rows, nq, nkv, bt_width, page_size, scale, window, ctas, err, s);
+  return launch_stream<64>(mk, mv, q, q_row_stride, out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
+                           rows, nq, nkv, bt_width, page_size, scale, window, ctas, err, s);
+}

@@ -292,35 +292,43 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
     if (csize > 8) return ARLE_E_UNSUPPORTED;
     KS = ((K + csize - 1) / csize + 31) / 32 * 32;
   }
-  const size_t smem = smem_bytes<NT, KB, SLOTS>(KS);
   auto kern = skinny_gemm_kernel<NT, KB, SLOTS, OutT>;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<NT, KB, SLOTS>(KS));
   if (e != cudaSuccess) return (int)e;
-  // a persistent grid must be resident at once: as many clusters as the GPU can hold together
-  int groups = sms / csize;
+  // A persistent grid must be resident at once: as many clusters as the GPU can hold together.
+  // Clusters do not span GPCs, so one size may leave more SMs idle than the next: of the
+  // smallest size that fits and the one above it, take the one that fills more SMs.
+  int groups = sms;
   if (csize > 1) {
-    static int cached[9][4] = {};                       // [cluster size][NT + 2 * (out is float)]
-    int& slot = cached[csize][(NT - 1) + 2 * (sizeof(OutT) == 4 ? 1 : 0)];
-    if (slot == 0) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(groups * csize);
-      cfg.blockDim = dim3(kThreads);
-      cfg.dynamicSmemBytes = smem;
-      cfg.stream = s;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeClusterDimension;
-      attr[0].val.clusterDim.x = csize;
-      attr[0].val.clusterDim.y = 1;
-      attr[0].val.clusterDim.z = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      int max_clusters = 0;
-      e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
-      if (e != cudaSuccess) return (int)e;
-      slot = max_clusters > 0 ? max_clusters : 1;
+    static int resident[10] = {};                       // clusters of each size that run together (this instantiation)
+    int best = csize, best_sms = 0;
+    for (int c = csize; c <= csize + 1 && c <= 8; ++c) {
+      if (resident[c] == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(sms / c * c);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem_bytes<NT, KB, SLOTS>(((K + c - 1) / c + 31) / 32 * 32);
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = c;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int max_clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+        if (e != cudaSuccess) return (int)e;
+        resident[c] = max_clusters > 0 ? max_clusters : 1;
+      }
+      const int filled = (resident[c] < sms / c ? resident[c] : sms / c) * c;
+      if (filled > best_sms + 2) best = c, best_sms = filled;   // a larger cluster must win by more than 2 SMs
     }
-    if (groups > slot) groups = slot;
+    csize = best;
+    KS = ((K + csize - 1) / csize + 31) / 32 * 32;
+    groups = resident[csize] < sms / csize ? resident[csize] : sms / csize;
   }
+  const size_t smem = smem_bytes<NT, KB, SLOTS>(KS);
   const int tiles = (N + 15) / 16;
   if (groups > tiles) groups = tiles;
   if (groups < 1) groups = 1;

@@ -46,6 +46,8 @@ _SIGNATURES = {
     "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
     "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
+                                           _F, _I, _I, _I, _P, _P],
     "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I,
                                         _I, _I, _P, _P],
@@ -325,7 +327,15 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
             prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
             prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
                     window, batch.max_q_len, skip_single=batch.num_single > 0)
-        if batch.num_single > 0:
+        if batch.num_single > 0 and stream_decode_supported(batch.num_rows, page_size):
+            ctas = sm_count(q.device)
+            slots = (ctas + batch.num_rows * nkv) * (nq // nkv)
+            paged_attention_decode_stream(
+                q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale, window,
+                batch.ws.get("attn_piece_o", (slots * hd,), torch.float32),
+                batch.ws.get("attn_piece_ml", (slots * 2,), torch.float32),
+                batch.ws.get_zeroed("attn_piece_counters", (batch.num_rows * nkv,), torch.int32), ctas)
+        elif batch.num_single > 0:
             splits = decode_splits(batch.num_rows, nkv, block_table.shape[1] * page_size)
             part_o = part_ml = counters = None
             if splits > 1:
@@ -367,6 +377,45 @@ def paged_attention_prefill_tc(q, out, k_cache, v_cache, q_indptr, kv_lens, bloc
         _ptr(kv_lens), _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
         int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _ptr(error_flag(q.device)), _stream()),
         "paged_attention_prefill_tc")
+
+
+_SM_COUNT: dict = {}
+
+
+def sm_count(device) -> int:
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _SM_COUNT[key]
+
+
+def stream_decode_supported(rows: int, page_size: int) -> bool:
+    """The streaming decode kernel fetches keys in TMA boxes of 16: pages must be
+    multiples of 16; its row table lives in shared memory: up to 2,048 rows."""
+    return page_size % 16 == 0 and rows <= 2048
+
+
+def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
+                                  window, piece_o, piece_ml, counters, ctas: int) -> None:
+    """Attention of the rows that have exactly one query (others are skipped), as a
+    resident grid of ``ctas`` CTAs that share the batch's 64-key tiles evenly.
+    Scratch: piece_o float32 [(ctas + R*nkv) * (nq/nkv) * hd], piece_ml float32
+    [(ctas + R*nkv) * (nq/nkv) * 2], counters int32 [R*nkv], zero before the first
+    launch (the kernel leaves it zero)."""
+    R = kv_lens.numel()
+    slots = (ctas + R * nkv) * (nq // nkv)
+    if (piece_o.numel() < slots * hd or piece_ml.numel() < slots * 2 or counters.numel() < R * nkv
+            or piece_o.dtype != torch.float32 or piece_ml.dtype != torch.float32 or counters.dtype != torch.int32):
+        raise KernelError("paged_attention_decode_stream: scratch for the pieces is missing or too small")
+    if q.dtype != torch.bfloat16 or q.stride(1) != 1 or not out.is_contiguous():
+        raise KernelError("paged_attention_decode_stream: needs bfloat16 queries with unit inner stride")
+    _i32(q_indptr, "q_indptr"), _i32(kv_lens, "kv_lens"), _i32(block_table, "block_table")
+    _check(library().arle_paged_attention_decode_stream(
+        _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(q_indptr), _ptr(kv_lens),
+        _ptr(block_table), block_table.stride(0), block_table.shape[1], _ptr(piece_o), _ptr(piece_ml), _ptr(counters),
+        nq, nkv, hd, page_size, float(scale), int(window) if window else 0, R, int(ctas), _ptr(error_flag(q.device)),
+        _stream()), "paged_attention_decode_stream")
 
 
 def decode_splits(rows: int, nkv: int, kv_bound: int) -> int:

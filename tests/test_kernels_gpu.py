@@ -364,6 +364,64 @@ def test_decode_attention_kernel(nq, nkv, hd, ps, window, splits):
         assert cnt.abs().sum().item() == 0
 
 
+def _stream_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, window, ctas, scratch=None):
+    R = kv.numel()
+    slots = (ctas + R * nkv) * (nq // nkv)
+    if scratch is None:
+        scratch = (torch.full((slots * hd,), float("nan"), device=DEV), torch.full((slots * 2,), float("nan"), device=DEV),
+                   torch.zeros(R * nkv, dtype=torch.int32, device=DEV))
+    ops.paged_attention_decode_stream(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, *scratch, ctas)
+    ops.check_errors(DEV)
+    return scratch
+
+
+@pytest.mark.parametrize("ctas", [1, 3, 37, 148, 400])
+@pytest.mark.parametrize("nq,nkv,hd,ps,window", [(32, 8, 128, 16, None), (6, 1, 64, 16, None), (16, 1, 128, 32, None),
+                                                  (4, 4, 128, 16, 100), (8, 2, 64, 48, 33), (3, 1, 128, 64, 700),
+                                                  (10, 2, 64, 16, 64)])
+def test_decode_attention_stream_kernel(nq, nkv, hd, ps, window, ctas):
+    """Every way of sharing the tiles among CTAs (one CTA alone, pieces of several pairs in one
+    CTA, a pair spread over many CTAs, more CTAs than tiles) gives the same attention."""
+    lens = [1, 63, 64, 65, 700, 2049, 17, 128]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, [1] * len(lens), seed=3)
+    out = torch.zeros(len(lens), nq * hd, dtype=torch.bfloat16, device=DEV)
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, window)
+    scratch = None
+    for _ in range(2):                      # twice: the counters must be back at zero after a launch
+        out.zero_()
+        scratch = _stream_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, window, ctas, scratch)
+        torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
+        assert scratch[2].abs().sum().item() == 0
+
+
+def test_decode_attention_stream_skips_prompt_rows_and_stale_slots():
+    """Rows with several queries are left alone, and cache slots beyond a request's last
+    key, holding huge values, do not leak through P = 0."""
+    nq, nkv, hd, ps = 8, 2, 128, 16
+    lens, q_lens = [100, 40, 7, 300, 1], [1, 40, 1, 11, 1]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=5)
+    used = torch.zeros(kc.shape[0], ps, dtype=torch.bool)
+    for r, n in enumerate(lens):
+        for j in range(n):
+            used[int(bt[r, j // ps]), j % ps] = True
+    vc[~used.to(DEV)[:, None, :].expand(-1, nkv, -1)] = 3.0e38
+    kc[~used.to(DEV)[:, None, :].expand(-1, nkv, -1)] = 3.0e38
+    out = torch.full((q.shape[0], nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _stream_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, None, 148)
+    single = torch.tensor([0, 41, 53])
+    assert out[1:41].isnan().all() and out[42:53].isnan().all()
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, None)
+    assert torch.isfinite(out[single.to(DEV)].float()).all()
+    torch.testing.assert_close(out[single.to(DEV)].float().cpu(), exp[single], rtol=2e-2, atol=1e-2)
+
+
+def test_decode_attention_stream_refuses_small_pages():
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(4, 2, 128, 8, [30], [1], seed=1)
+    out = torch.zeros(1, 4 * 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.KernelError):
+        _stream_decode(q, out, kc, vc, qi, kv, bt, 4, 2, 128, 8, None, 8)
+
+
 @pytest.mark.parametrize("nq,nkv,hd,ps,window", [(32, 8, 128, 16, None), (6, 1, 64, 8, None), (4, 4, 128, 16, 70),
                                                   (8, 2, 64, 4, 33), (3, 1, 128, 5, 64), (2, 1, 128, 64, 65)])
 def test_prefill_attention_kernel(nq, nkv, hd, ps, window):
@@ -419,7 +477,7 @@ def test_prefill_and_decode_kernels_split_a_mixed_step():
     torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
 
 
-@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+@pytest.mark.parametrize("kernel", ["decode", "stream", "prefill"])
 def test_fast_attention_sees_one_far_key_and_the_windows_edge(kernel):
     """Peaked attention: the query is aligned with exactly one key far back, so the
     output must be that key's value; with a window that ends one key short of it,
@@ -427,7 +485,7 @@ def test_fast_attention_sees_one_far_key_and_the_windows_edge(kernel):
     nq, nkv, hd, ps = 4, 1, 128, 16
     n = 1000
     for far in (0, 63, 64, 500, 998):
-        lens, q_lens = ([n], [1]) if kernel == "decode" else ([n], [3])
+        lens, q_lens = ([n], [3]) if kernel == "prefill" else ([n], [1])
         q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=far)
         page, off = int(bt[0, far // ps]), far % ps
         unit = torch.zeros(hd)
@@ -440,6 +498,8 @@ def test_fast_attention_sees_one_far_key_and_the_windows_edge(kernel):
                 ops.paged_attention_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, 4,
                                            torch.empty(nq * 4 * hd, device=DEV), torch.empty(nq * 8, device=DEV),
                                            torch.zeros(nkv, dtype=torch.int32, device=DEV))
+            elif kernel == "stream":
+                _stream_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, window, 5)
             else:
                 ops.paged_attention_prefill(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, 3)
             close = (out[-1, :hd].float() - vc[page, 0, off].float()).abs().max().item() < 2e-2
