@@ -84,8 +84,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-// 1: kernels are launched with programmatic stream serialisation allowed.  Off by
-// default: inside captured CUDA graphs it measured slower than stream-order launches.
+// Bit 0: every kernel is launched with programmatic stream serialisation allowed; bit 1:
+// the weight-streaming products only (they fill their weight ring while the kernel before
+// them finishes).  Off by default.
 inline int& pdl_enabled() {
   static int on = 0;
   return on;
@@ -94,8 +95,8 @@ inline int& pdl_enabled() {
 // kernel<<<grid, block, smem, stream>>>(args...) with the programmatic-launch attribute
 // (and a cluster dimension when cluster > 1).
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                 int cluster, Args&&... args) {
+inline cudaError_t launch_kernel_as(bool programmatic, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, int cluster, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -103,7 +104,7 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int n = 0;
-  if (pdl_enabled()) {
+  if (programmatic) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
@@ -118,6 +119,12 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.attrs = attr;
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 int cluster, Args&&... args) {
+  return launch_kernel_as((pdl_enabled() & 1) != 0, kernel, grid, block, smem, stream, cluster, std::forward<Args>(args)...);
 }
 
 inline int launch_status() {

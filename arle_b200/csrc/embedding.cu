@@ -74,4 +74,4 @@ ARLE_API int arle_embedding(const int* ids, const void* table, int table_dtype, 
 
 // 1: kernels are launched so that the next kernel of the stream may start its set-up
 // (barriers, weight prefetch) while the previous one finishes; 0 (default): plain launches.
-ARLE_API void arle_set_programmatic_launch(int on) { arle::pdl_enabled() = on ? 1 : 0; }
+ARLE_API void arle_set_programmatic_launch(int mode) { arle::pdl_enabled() = mode & 3; }

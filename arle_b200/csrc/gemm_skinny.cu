@@ -332,8 +332,9 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
   const int tiles = (N + 15) / 16;
   if (groups > tiles) groups = tiles;
   if (groups < 1) groups = 1;
-  e = launch_kernel(kern, dim3(groups * csize), dim3(kThreads), smem, s, csize, (const __nv_bfloat16*)x, ldx,
-                    (const __nv_bfloat16*)W, ldw, (OutT*)out, ldo, M, N, K, KS, csize, pdl_enabled(), err);
+  const bool early = (pdl_enabled() & 3) != 0;
+  e = launch_kernel_as(early, kern, dim3(groups * csize), dim3(kThreads), smem, s, csize, (const __nv_bfloat16*)x, ldx,
+                       (const __nv_bfloat16*)W, ldw, (OutT*)out, ldo, M, N, K, KS, csize, early ? 1 : 0, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }

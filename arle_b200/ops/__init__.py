@@ -99,14 +99,15 @@ def check_errors(device) -> None:
         raise KernelError("a kernel gave up a bounded wait (asynchronous copy did not complete); results are invalid")
 
 
-def set_programmatic_launch(on: bool) -> None:
+def set_programmatic_launch(on) -> None:
     """Programmatic dependent launch (off by default): a kernel may be scheduled, set up
     its barriers and prefetch weights while the kernel before it finishes, and waits
-    for that kernel only before touching its results."""
+    for that kernel only before touching its results.  True or 1: every kernel; 2: the
+    weight-streaming products only."""
     lib = library()
     lib.arle_set_programmatic_launch.argtypes = [c_int]
     lib.arle_set_programmatic_launch.restype = None
-    lib.arle_set_programmatic_launch(1 if on else 0)
+    lib.arle_set_programmatic_launch(int(on))
 
 
 def _dt(t: torch.Tensor) -> int:

@@ -101,7 +101,8 @@ def main() -> int:
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="profiling aid: run only the decode steps at --batch, or only the prefill")
     ap.add_argument("--no-cuda-graph", action="store_true")
-    ap.add_argument("--pdl", action="store_true", help="launch kernels with programmatic dependent launch")
+    ap.add_argument("--pdl", type=int, nargs="?", const=1, default=0,
+                    help="programmatic dependent launch: 1 every kernel, 2 the weight-streaming products only")
     ap.add_argument("--tcgen05-gemm", action="store_true", help="products of 128 rows and more through the package's tcgen05 kernel instead of cuBLAS")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -124,7 +125,7 @@ def main() -> int:
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     if args.pdl:
-        ops.set_programmatic_launch(True)
+        ops.set_programmatic_launch(args.pdl)
     if args.tcgen05_gemm:
         ops.set_tcgen05_min_rows(128)
     pk = peaks()
