@@ -1,6 +1,6 @@
-// SwiGLU gate: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(g) = g / (1 + exp(-g)),
+// SwiGLU gate: out[t, i] = silu(gu[t, 2i]) * gu[t, 2i + 1], silu(g) = g / (1 + exp(-g)),
 // computed in float32 and rounded once.  gu is the [T, 2I] output of the packed
-// gate/up projection.
+// gate/up projection, whose rows 2i and 2i + 1 are gate_i and up_i.
 #include "common.cuh"
 using namespace arle;
 
@@ -12,8 +12,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / inter;
     const int i = (int)(idx - t * inter);
-    const float g = to_f32(gu[t * 2 * (size_t)inter + i]);
-    const float u = to_f32(gu[t * 2 * (size_t)inter + inter + i]);
+    const float g = to_f32(gu[t * 2 * (size_t)inter + 2 * i]);
+    const float u = to_f32(gu[t * 2 * (size_t)inter + 2 * i + 1]);
     out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
   }
 }
@@ -27,17 +27,17 @@ __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, _
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / i8;
     const int c = (int)(idx - t * i8);
-    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter + 8 * c);
-    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter + inter + 8 * c);
-    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
-    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    const uint4 a4 = *reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter + 16 * c);       // pairs 0..3
+    const uint4 b4 = *reinterpret_cast<const uint4*>(gu + t * 2 * (size_t)inter + 16 * c + 8);   // pairs 4..7
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a4);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b4);
     uint4 o4;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const float ga = __low2float(g2[k]), gb = __high2float(g2[k]);
-      o2[k] = __floats2bfloat162_rn(ga / (1.0f + expf(-ga)) * __low2float(u2[k]),
-                                    gb / (1.0f + expf(-gb)) * __high2float(u2[k]));
+      const __nv_bfloat162 p0 = k < 2 ? a2[2 * k] : b2[2 * k - 4], p1 = k < 2 ? a2[2 * k + 1] : b2[2 * k - 3];
+      const float ga = __low2float(p0), gb = __low2float(p1);
+      o2[k] = __floats2bfloat162_rn(ga / (1.0f + expf(-ga)) * __high2float(p0), gb / (1.0f + expf(-gb)) * __high2float(p1));
     }
     *reinterpret_cast<uint4*>(out + t * (size_t)inter + 8 * c) = o4;
   }

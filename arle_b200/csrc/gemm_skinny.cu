@@ -72,7 +72,7 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 template <int NT, int KB, int SLOTS, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W, int ldw, OutT* __restrict__ out,
-    int ldo, int M, int N, int K, int KS, int csize, int early, int* __restrict__ err) {
+    int ldo, int M, int N, int K, int KS, int csize, int early, int gated, int* __restrict__ err) {
   constexpr int PITCH = KB * 2 + kRowPad;                 // bytes per weight-row segment in a stage
   constexpr int STAGE = 16 * PITCH;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -93,8 +93,10 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
   const int g = lane >> 2, tq = lane & 3;
   const int rank = csize > 1 ? (int)(blockIdx.x % csize) : 0;
   const int group = blockIdx.x / csize, ngroups = gridDim.x / csize;
-  const int r0 = (int)((long long)N * group / ngroups);
-  const int r1 = (int)((long long)N * (group + 1) / ngroups);
+  // gated: weight rows come in (gate, up) pairs that stay in one CTA and one tile
+  const int unit = gated ? 2 : 1;
+  const int r0 = (int)((long long)(N / unit) * group / ngroups) * unit;
+  const int r1 = (int)((long long)(N / unit) * (group + 1) / ngroups) * unit;
   const int ks0 = rank * KS;
   const int ks1 = min(K, ks0 + KS);
   const int klen = max(0, ks1 - ks0);
@@ -224,7 +226,12 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) s += rb[(size_t)w * 16 * NT * 8];
-      if (csize == 1) {
+      if (gated) {
+        // rows 2i and 2i+1 of W are gate_i and up_i: out[m, i] = silu(gate) * up, in float32
+        const float up = __shfl_down_sync(0xffffffffu, s, 1);
+        if (!(row & 1) && m < M && rt + row < r1)
+          store_out<OutT>(out + (size_t)m * ldo + ((rt + row) >> 1), s / (1.0f + expf(-s)) * up);
+      } else if (csize == 1) {
         if (m < M && rt + row < r1) store_out<OutT>(out + (size_t)m * ldo + rt + row, s);
       } else {
         part[(batched ? tile : (tile & 1)) * 16 * NT * 8 + tid] = s;
@@ -277,8 +284,8 @@ size_t smem_bytes(int KS) {
 }
 
 template <int NT, int KB, int SLOTS, typename OutT>
-int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int* err,
-                    cudaStream_t s) {
+int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int gated,
+                    int* err, cudaStream_t s) {
   int dev = 0, sms = 0, max_smem = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
@@ -292,6 +299,7 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
     if (csize > 8) return ARLE_E_UNSUPPORTED;
     KS = ((K + csize - 1) / csize + 31) / 32 * 32;
   }
+  if (gated && csize > 1) return ARLE_E_UNSUPPORTED;       // the gate needs whole sums in one CTA
   auto kern = skinny_gemm_kernel<NT, KB, SLOTS, OutT>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<NT, KB, SLOTS>(KS));
   if (e != cudaSuccess) return (int)e;
@@ -334,9 +342,25 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
   if (groups < 1) groups = 1;
   const bool early = (pdl_enabled() & 3) != 0;
   e = launch_kernel_as(early, kern, dim3(groups * csize), dim3(kThreads), smem, s, csize, (const __nv_bfloat16*)x, ldx,
-                       (const __nv_bfloat16*)W, ldw, (OutT*)out, ldo, M, N, K, KS, csize, early ? 1 : 0, err);
+                       (const __nv_bfloat16*)W, ldw, (OutT*)out, ldo, M, N, K, KS, csize, early ? 1 : 0, gated, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
+}
+
+int skinny_entry(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N, int K,
+                 int gated, int* err, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return ARLE_E_UNSUPPORTED;
+  if (((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return ARLE_E_UNSUPPORTED;
+  if (gated && N % 2 != 0) return ARLE_E_BADARG;
+  if (M <= 8) {
+    if (out_dtype == 0) return plan_and_launch<1, 256, 2, float>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
+    if (out_dtype == 1) return plan_and_launch<1, 256, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
+  } else {
+    if (out_dtype == 0) return plan_and_launch<2, 256, 2, float>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
+    if (out_dtype == 1) return plan_and_launch<2, 256, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
+  }
+  return ARLE_E_BADARG;
 }
 
 }  // namespace
@@ -345,15 +369,13 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
 // 16-byte aligned x and W.  err (may be null): set to 1 if a bounded wait ran out.
 ARLE_API int arle_gemm_skinny(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M, int N,
                               int K, int* err, cudaStream_t s) {
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 16 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return ARLE_E_UNSUPPORTED;
-  if (((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return ARLE_E_UNSUPPORTED;
-  if (M <= 8) {
-    if (out_dtype == 0) return plan_and_launch<1, 256, 2, float>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
-    if (out_dtype == 1) return plan_and_launch<1, 256, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
-  } else {
-    if (out_dtype == 0) return plan_and_launch<2, 256, 2, float>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
-    if (out_dtype == 1) return plan_and_launch<2, 256, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, err, s);
-  }
-  return ARLE_E_BADARG;
+  return skinny_entry(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, 0, err, s);
+}
+
+// The gated feed-forward's first half in one launch: W [N, K] holds (gate_i, up_i) in rows 2i and
+// 2i + 1, and out[M, N / 2] = silu(x . gate_i) * (x . up_i), the gate computed on the float32 sums.
+// Same needs as arle_gemm_skinny, and a K short enough for x to stay in one CTA's shared memory.
+ARLE_API int arle_gemm_skinny_gated(const void* x, int ldx, const void* W, int ldw, void* out, int out_dtype, int ldo, int M,
+                                    int N, int K, int* err, cudaStream_t s) {
+  return skinny_entry(x, ldx, W, ldw, out, out_dtype, ldo, M, N, K, 1, err, s);
 }

@@ -53,6 +53,7 @@ _SIGNATURES = {
                                         _I, _I, _P, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_skinny": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+    "arle_gemm_skinny_gated": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_argmax": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "arle_scatter_tokens": [_P, _P, _P, _I, _P],
@@ -462,8 +463,33 @@ def paged_attention_prefill(q, out, k_cache, v_cache, q_indptr, kv_lens, block_t
 
 
 # ------------------------------------------------------------------ activation
+def gemm_silu_mul(x: torch.Tensor, w: torch.Tensor, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """The first half of a gated feed-forward: out[t, i] = silu(x[t] . w[2i]) * (x[t] . w[2i + 1]) for
+    w [2I, K] whose rows 2i and 2i + 1 are gate_i and up_i.  Few rows of x take one launch of
+    the weight-streaming kernel (the gate applied to its float32 sums); otherwise the product
+    goes to ``gate_up`` [T, 2I] and ``silu_mul`` follows."""
+    T, I = out.shape
+    if w.shape[0] != 2 * I or gate_up.shape != (T, 2 * I):
+        raise KernelError(f"gemm_silu_mul: shapes w {tuple(w.shape)} gate_up {tuple(gate_up.shape)} out {tuple(out.shape)}")
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and skinny_gemm_supported(x, w, out)
+            and gated_gemm_fits(x.shape[1])):
+        _ptr(x), _ptr(w), _ptr(out)
+        _check(library().arle_gemm_skinny_gated(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out), out.stride(0),
+                                                T, 2 * I, x.shape[1], _ptr(error_flag(x.device)), _stream()),
+               "gemm_skinny_gated")
+        return
+    gemm(x, w, gate_up)
+    silu_mul(gate_up, out)
+
+
+def gated_gemm_fits(K: int) -> bool:
+    """The gate needs whole sums in one CTA: 8 rows of x (K + 8 elements each) must fit in
+    shared memory beside the weight ring (about 150 KB of the 227 KB)."""
+    return 16 * (K + 8) <= 72 * 1024
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]; gate_up [T, 2I], out [T, I]."""
+    """out[t, i] = silu(gate_up[t, 2i]) * gate_up[t, 2i + 1]; gate_up [T, 2I], out [T, I]."""
     T, I = out.shape
     if gate_up.shape != (T, 2 * I) or not gate_up.is_contiguous() or not out.is_contiguous() or gate_up.dtype != out.dtype:
         raise KernelError("silu_mul: gate_up must be contiguous [T, 2I] and out contiguous [T, I] of one type")

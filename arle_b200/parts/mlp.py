@@ -1,7 +1,8 @@
 """Gated feed-forward (SwiGLU): down(act(gate(x)) * up(x)), no biases
-(infer/src/model/qwen3/prefill.rs:291-337).  Gate and up are packed row-wise into
-one [2I, H] matrix at load, the layout cklxx/arle offers as an option
-(infer/src/model/qwen3/weights.rs:98-122)."""
+(infer/src/model/qwen3/prefill.rs:291-337).  Gate and up are packed into one [2I, H]
+matrix at load (cklxx/arle offers a packed layout as an option,
+infer/src/model/qwen3/weights.rs:98-122); here row 2i is gate_i and row 2i + 1 is up_i, so
+that the kernel that forms both sums of a pair can apply the gate itself."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -40,7 +41,8 @@ class GatedMlp(FeedForward):
         p = self.spec.prefix
         g, u, d = (tensors[p + n + "_proj.weight"] for n in ("gate", "up", "down"))
         wt = dtype if dtype == torch.bfloat16 else (torch.float32 if torch.float32 in (g.dtype, u.dtype) else torch.bfloat16)
-        self.w_gate_up = torch.cat([g.to(device=device, dtype=wt), u.to(device=device, dtype=wt)], dim=0).contiguous()
+        g, u = g.to(device=device, dtype=wt), u.to(device=device, dtype=wt)
+        self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
         self.w_down = d.to(device=device, dtype=dtype if dtype == torch.bfloat16 else d.dtype).contiguous()
 
     def weight_bytes(self):
@@ -50,9 +52,8 @@ class GatedMlp(FeedForward):
         s = self.spec
         T = x.shape[0]
         gu = ctx.ws.get("gate_up", (T, 2 * s.intermediate_size), x.dtype)
-        ops.gemm(x, self.w_gate_up, gu)
         act = ctx.ws.get("ffn_act", (T, s.intermediate_size), x.dtype)
-        ops.silu_mul(gu, act)
+        ops.gemm_silu_mul(x, self.w_gate_up, gu, act)
         out = ctx.ws.get("ffn_out", (T, s.hidden_size), x.dtype)
         ops.gemm(act, self.w_down, out)
         return out

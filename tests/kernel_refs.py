@@ -92,9 +92,13 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
 
 
 def silu_mul(gate_up, out):
-    I = out.shape[1]
-    g, u = gate_up[:, :I].to(F32), gate_up[:, I:].to(F32)
+    g, u = gate_up[:, 0::2].to(F32), gate_up[:, 1::2].to(F32)          # rows 2i, 2i + 1 of the packed weight: gate_i, up_i
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+
+
+def gemm_silu_mul(x, w, gate_up, out):
+    gemm(x, w, gate_up)
+    silu_mul(gate_up, out)
 
 
 def argmax(logits, scratch, out, scatter=None, last_token=None):
@@ -138,4 +142,4 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out):
         out[r] = int(hit[0]) if hit.numel() else int(torch.nonzero(p > 0)[-1])
 
 
-ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "attention_prep", "paged_attention", "silu_mul", "argmax", "scatter_tokens", "sample")
+ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample")

@@ -147,6 +147,33 @@ def test_gemm_skinny_weight_streaming(M, N, K, out_dtype):
     ops.check_errors(DEV)                       # no bounded wait ran out
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,I,K", [(1, 8, 32), (8, 12288, 4096), (3, 500, 192), (5, 37, 320), (8, 2050, 4096), (7, 100, 4608),
+                                   (9, 64, 64), (40, 176, 96), (2, 64, 8192)])
+def test_gemm_silu_mul(M, I, K, out_dtype):
+    """Gate and up rows interleaved in one weight; few rows of x take the fused launch, more rows
+    (or a K too long for one CTA) the product and the gate kernel: same numbers either way."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(2 * I, K, dtype=torch.bfloat16, scale=0.08, seed=2)
+    gu = torch.full((M, 2 * I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = torch.full((M, I), float("nan"), dtype=out_dtype, device=DEV)
+    fused = M <= 8 and ops.gated_gemm_fits(K)
+    before = ops.launch_count()
+    if out_dtype == torch.float32 and not fused:
+        pytest.skip("the two-kernel path writes the activation type")
+    ops.gemm_silu_mul(x, w, gu, out)
+    assert ops.launch_count() - before == (1 if fused else (2 if M <= 8 else 1))
+    ops.check_errors(DEV)
+    g = x.double() @ w[0::2].double().t()
+    u = x.double() @ w[1::2].double().t()
+    exp = g / (1 + torch.exp(-g)) * u
+    err = (out.double() - exp).abs().max().item()
+    scale = exp.abs().max().item()
+    assert err <= (3e-5 if out_dtype == torch.float32 else 1.5e-2) * max(scale, 1.0), (err, scale)
+    if fused:
+        assert gu.isnan().all()                    # the product itself was never written
+
+
 def test_gemm_skinny_takes_row_views():
     big = rnd(8, 512, dtype=torch.bfloat16, seed=3)
     x, w = big[:, :256], rnd(70, 256, dtype=torch.bfloat16, seed=4)      # row stride 512, unit inner stride
