@@ -78,8 +78,8 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t l
 __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, const int* __restrict__ q_indptr,
-    const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride, int nq, int nkv, int page_size,
-    float scale_log2, int window, int skip_single, int* __restrict__ err) {
+    const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride, int bt_width, int nq, int nkv,
+    int page_size, float scale_log2, int window, int skip_single, int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.z, h = blockIdx.y;
@@ -156,14 +156,27 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     const int c = (lane >> 1) & 7, half = lane & 1;      // page of the tile, half of the head (lanes 0..15)
     const CUtensorMap* map = keys ? &map_k : &map_v;
     unsigned char* tile_s = keys ? k_s : v_s;
+    // Page ids come 32 at a time, one per lane, with the next 32 already in flight, so that no
+    // tile waits for a read of the block table; a lane picks its page with a shuffle.
+    int p0 = kb / page_size;
+    int cur = __ldg(bt + min(p0 + lane, bt_width - 1));
+    int nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
     for (int j = 0; j < ntiles; ++j) {
       const int st = j & 1;
       const uint32_t par = (uint32_t)((j >> 1) & 1);
       const int key0 = kb + j * BKV + c * 16;
+      while ((kb + j * BKV) / page_size - p0 >= 32) {
+        cur = nxt;
+        p0 += 32;
+        nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
+      }
+      const int pi = key0 / page_size;
+      const int rel = pi - p0;                                // 0 .. 63: a tile spans at most 8 pages
+      const int from_cur = __shfl_sync(0xffffffffu, cur, rel & 31), from_nxt = __shfl_sync(0xffffffffu, nxt, rel & 31);
       int row = -1;
       if (lane < 16 && key0 <= p_last && key0 + 15 >= lo) {
-        const int page = bt[key0 / page_size];
-        row = (page * nkv + kvh) * page_size + key0 % page_size;
+        const int page = rel < 32 ? from_cur : from_nxt;
+        row = (page * nkv + kvh) * page_size + (key0 - pi * page_size);
       }
       const int n = __popc(__ballot_sync(0xffffffffu, row >= 0)) >> 1;      // pages of this tile
       uint64_t* full = keys ? &k_full[st] : &v_full[st];
@@ -369,10 +382,11 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
 // q_row_stride % 8 == 0, 16-byte aligned q, and out rows of nq * 128 elements.
 ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, int num_tokens, void* out, const void* k_cache,
                                              const void* v_cache, long long cache_pages, const int* q_indptr,
-                                             const int* kv_lens, const int* block_table, int bt_stride, int nq, int nkv,
+                                             const int* kv_lens, const int* block_table, int bt_stride, int bt_width, int nq, int nkv,
                                              int hd, int page_size, float scale, int window, int rows, int max_q_len,
                                              int skip_single, int* err, cudaStream_t s) {
   if (rows <= 0 || max_q_len <= 0) return 0;
+  if (bt_width < 1) return ARLE_E_BADARG;
   if (hd != HD || page_size % 16 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq > 65535 || rows > 65535)
     return ARLE_E_UNSUPPORTED;
   if (q_row_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
@@ -394,7 +408,7 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
   }
   dim3 grid((max_q_len + BQ - 1) / BQ, nq, rows);
   cudaError_t e = launch_kernel(paged_prefill_tc_kernel, grid, dim3(kThreads), smem, s, 1, mq, mk, mv, (__nv_bfloat16*)out,
-                                q_indptr, kv_lens, block_table, bt_stride, nq, nkv, page_size,
+                                q_indptr, kv_lens, block_table, bt_stride, bt_width, nq, nkv, page_size,
                                 scale * 1.4426950408889634f, window, skip_single, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();

@@ -49,8 +49,8 @@ _SIGNATURES = {
     "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
                                            _F, _I, _I, _I, _P, _P],
     "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
-    "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I,
-                                        _I, _I, _P, _P],
+    "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I,
+                                        _I, _I, _I, _P, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_skinny": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_gemm_skinny_gated": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -82,10 +82,18 @@ def library() -> ctypes.CDLL:
 _ERR_FLAGS = {}
 
 
+def _device_key(device) -> torch.device:
+    """"cuda" and "cuda:0" name the same device: always the indexed form."""
+    d = torch.device(device)
+    if d.type == "cuda" and d.index is None:
+        d = torch.device("cuda", torch.cuda.current_device())
+    return d
+
+
 def error_flag(device) -> torch.Tensor:
     """The device word that kernels with bounded waits raise when a wait ran out
     (one int32 per device, made at first use)."""
-    key = torch.device(device)
+    key = _device_key(device)
     if key not in _ERR_FLAGS:
         _ERR_FLAGS[key] = torch.zeros(1, dtype=torch.int32, device=key)
     return _ERR_FLAGS[key]
@@ -94,10 +102,13 @@ def error_flag(device) -> torch.Tensor:
 def check_errors(device) -> None:
     """Reads the error word (a device synchronisation) and raises if a kernel gave
     up waiting; the word is cleared."""
-    key = torch.device(device)
-    if key in _ERR_FLAGS and int(_ERR_FLAGS[key].item()) != 0:
-        _ERR_FLAGS[key].zero_()
-        raise KernelError("a kernel gave up a bounded wait (asynchronous copy did not complete); results are invalid")
+    key = _device_key(device)
+    if key in _ERR_FLAGS:
+        code = int(_ERR_FLAGS[key].item())
+        if code != 0:
+            _ERR_FLAGS[key].zero_()
+            raise KernelError(f"a kernel gave up a bounded wait (code {code}: an asynchronous copy or a tensor-core "
+                              "operation did not complete); results are invalid")
 
 
 def set_programmatic_launch(on) -> None:
@@ -376,7 +387,7 @@ def paged_attention_prefill_tc(q, out, k_cache, v_cache, q_indptr, kv_lens, bloc
         raise KernelError("paged_attention_prefill_tc: needs bfloat16, head size 128, page size a multiple of 16")
     _check(library().arle_paged_attention_prefill_tc(
         _ptr(q), q.stride(0), q.shape[0], _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(q_indptr),
-        _ptr(kv_lens), _ptr(block_table), block_table.stride(0), nq, nkv, hd, page_size, float(scale),
+        _ptr(kv_lens), _ptr(block_table), block_table.stride(0), block_table.shape[1], nq, nkv, hd, page_size, float(scale),
         int(window) if window else 0, R, int(max_q_len), int(bool(skip_single)), _ptr(error_flag(q.device)), _stream()),
         "paged_attention_prefill_tc")
 
