@@ -4,10 +4,11 @@
 // One CTA serves 128 consecutive queries of one request and one query head and walks
 // the visible keys in tiles of 128 (boundaries at multiples of 128 of the absolute key
 // position).  Everything big lives where the tensor cores want it:
-//   shared memory : Q (128 x 128), two stages each of K, V (128 keys x 128) and P (128 x 128),
-//                   all in the 128-byte swizzled layout that TMA writes and tcgen05.mma reads;
-//   tensor memory : two buffers for the scores S (128 lanes x 128 columns, float32) and one
-//                   for the output accumulator O (128 x 128, float32).
+//   shared memory : Q (128 x 128) and three stages each of K and V (128 keys x 128), in the
+//                   128-byte swizzled layout that TMA writes and tcgen05.mma reads;
+//   tensor memory : two buffers for the scores S (128 lanes x 128 columns, float32), the
+//                   output accumulator O (128 x 128, float32) and two buffers for P
+//                   (128 lanes x 64 columns, two bfloat16 per column): all 512 columns.
 // Roles by warp:
 //   warps 4 and 6    : loaders (keys; values).  TMA tile loads (cp.async.bulk.tensor.2d): Q
 //                      once from the packed projection output, then per tile the keys or the
@@ -15,16 +16,17 @@
 //                      at the rows the block table names.
 //   warp 5, one lane : MMA issuer.  S(j) = Q . K(j)^T (eight tcgen05.mma of K 16, both operands
 //                      K-major) into S buffer j mod 2, one tile ahead of the softmax;
-//                      O += P(j) . V(j) (eight tcgen05.mma, V used as it lies in the cache:
-//                      an MN-major B operand).  tcgen05.commit signals the mbarriers.
+//                      O += P(j) . V(j) (eight tcgen05.mma with P as the A operand read from
+//                      tensor memory, and V used as it lies in the cache: an MN-major B
+//                      operand).  tcgen05.commit signals the mbarriers.
 //   warps 0-3        : softmax and epilogue; thread i owns query row i (TMEM lane i), so row
 //                      maxima and sums need no shuffles.  A thread reads its row of S into
 //                      registers, masks (key <= query position, and > position - window)
 //                      and finds the row maximum; O and the running sum are rescaled only
 //                      when the maximum grew by more than 2^8 since the last rescale (the
 //                      exponentials stay within float32 and bfloat16 range); then it
-//                      exponentiates, adds up and writes P as bfloat16 into shared memory
-//                      (two buffers), as cklxx/arle's prefill kernel rounds P
+//                      exponentiates, adds up and writes P as bfloat16 into tensor memory
+//                      (tcgen05.st, two buffers), as cklxx/arle's prefill kernel rounds P
 //                      (crates/cuda-kernels/tools/tilelang/batch_prefill_paged_hd128.py:223-225).
 //                      After the last tile the rows are divided by their sums and stored.
 // Scores, maxima, sums and the accumulator are float32.  Every mbarrier wait is bounded;
@@ -41,6 +43,7 @@ constexpr int BKV = 128;                     // keys per tile
 constexpr int kThreads = 224;
 constexpr uint32_t SUB = 128 * 128;          // bytes of a [128 rows x 64 elements] swizzled sub-tile
 constexpr uint32_t TILE = 2 * SUB;           // 128 x 128 bfloat16
+constexpr int kStages = 3;                   // stages of keys and of values
 constexpr float kRescaleStep = 8.0f;         // log2 units the maximum may grow before O is rescaled
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -51,6 +54,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+// tcgen05.mma with the A operand in tensor memory: lane = row of A, each 32-bit column holds two
+// consecutive bfloat16 elements of K (16 elements of K = 8 columns).
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ float ex2_fast(float x) {          // 2^x on the special-function unit; -inf gives 0
@@ -100,10 +110,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = base;                      // TILE
-  unsigned char* k_s = base + TILE;               // 2 x TILE
-  unsigned char* v_s = base + 3 * TILE;           // 2 x TILE
-  unsigned char* p_s = base + 5 * TILE;           // 2 x TILE: P of even and of odd tiles
-  __shared__ __align__(8) uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2],
+  unsigned char* k_s = base + TILE;                       // kStages x TILE
+  unsigned char* v_s = base + (1 + kStages) * TILE;       // kStages x TILE
+  __shared__ __align__(8) uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_empty[2], p_full[2],
       pv_done[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -111,11 +120,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(smem_addr(&q_full), 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kStages; ++i) {
       mbar_init(smem_addr(&k_full[i]), 1);
       mbar_init(smem_addr(&k_empty[i]), 1);
       mbar_init(smem_addr(&v_full[i]), 1);
       mbar_init(smem_addr(&v_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(smem_addr(&s_full[i]), 1);
       mbar_init(smem_addr(&s_empty[i]), 4);
     }
@@ -128,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   }
   // Value rows that no load ever fills (beyond the last key) meet P = 0; they must hold
   // numbers, not whatever bits shared memory had.
-  for (uint32_t i = threadIdx.x; i < 2 * TILE / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+  for (uint32_t i = threadIdx.x; i < kStages * TILE / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   if (warp == 5) {
     tmem_alloc(smem_addr(&tmem_base_slot), 512);
@@ -139,6 +150,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_p = tmem_base + 384;                    // two buffers of 64 columns: P as packed bfloat16 pairs
   const volatile int* aborted = &abort_flag;
 
   if (warp == 4 || warp == 6) {
@@ -162,8 +174,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     int cur = __ldg(bt + min(p0 + lane, bt_width - 1));
     int nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
     for (int j = 0; j < ntiles; ++j) {
-      const int st = j & 1;
-      const uint32_t par = (uint32_t)((j >> 1) & 1);
+      const int st = j % kStages;
+      const uint32_t par = (uint32_t)((j / kStages) & 1);
       const int key0 = kb + j * BKV + c * 16;
       while ((kb + j * BKV) / page_size - p0 >= 32) {
         cur = nxt;
@@ -199,19 +211,19 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       constexpr uint32_t idesc_pv = idesc_bf16(BQ, HD) | (1u << 16);    // B (values) MN-major
       bool ok = mbar_wait_bounded(smem_addr(&q_full), 0, aborted);
       auto issue_s = [&](int j) {
-        const int st = j & 1;
+        const int st = j & 1, kst = j % kStages;
         const uint32_t par = (uint32_t)((j >> 1) & 1);
-        if (!mbar_wait_bounded(smem_addr(&k_full[st]), par, aborted)) return false;
+        if (!mbar_wait_bounded(smem_addr(&k_full[kst]), (uint32_t)((j / kStages) & 1), aborted)) return false;
         if (!mbar_wait_bounded(smem_addr(&s_empty[st]), par ^ 1, aborted)) return false;
         tc_fence_after();
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh) {
           const uint64_t ad = smem_desc_sw128(smem_addr(q_s + dh * SUB));
-          const uint64_t bd = smem_desc_sw128(smem_addr(k_s + st * TILE + dh * SUB));
+          const uint64_t bd = smem_desc_sw128(smem_addr(k_s + kst * TILE + dh * SUB));
 #pragma unroll
           for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + (uint32_t)(st * BKV), ad + 2 * k, bd + 2 * k, idesc_s, (dh | k) != 0 ? 1u : 0u);
         }
-        umma_commit(smem_addr(&k_empty[st]));
+        umma_commit(smem_addr(&k_empty[kst]));
         umma_commit(smem_addr(&s_full[st]));
         return true;
       };
@@ -219,17 +231,16 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       for (int j = 0; j < ntiles && ok; ++j) {
         if (j + 1 < ntiles) ok = issue_s(j + 1);
         if (!ok) break;
-        const int st = j & 1;
+        const int st = j & 1, vst = j % kStages;
         if (!mbar_wait_bounded(smem_addr(&p_full[st]), (uint32_t)((j >> 1) & 1), aborted)) { ok = false; break; }
-        if (!mbar_wait_bounded(smem_addr(&v_full[st]), (uint32_t)((j >> 1) & 1), aborted)) { ok = false; break; }
+        if (!mbar_wait_bounded(smem_addr(&v_full[vst]), (uint32_t)((j / kStages) & 1), aborted)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t ad = smem_desc_sw128(smem_addr(p_s + st * TILE + (kk >> 2) * SUB)) + 2 * (kk & 3);
-          const uint64_t bd = smem_desc_mn_sw128(smem_addr(v_s + st * TILE + kk * 2048), SUB);
-          umma_bf16(tmem_o, ad, bd, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+          const uint64_t bd = smem_desc_mn_sw128(smem_addr(v_s + vst * TILE + kk * 2048), SUB);
+          umma_bf16_a_tmem(tmem_o, tmem_p + (uint32_t)(st * 64 + kk * 8), bd, idesc_pv, (j | kk) != 0 ? 1u : 0u);
         }
-        umma_commit(smem_addr(&v_empty[st]));
+        umma_commit(smem_addr(&v_empty[vst]));
         umma_commit(smem_addr(&pv_done[st]));
       }
       if (!ok) abort_flag = 1;
@@ -314,26 +325,22 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       // K-major layout
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t packed[16];
+      for (int h2 = 0; h2 < 2; ++h2) {
+        uint32_t packed[32];                                  // 64 keys of this row as bfloat16 pairs
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float e0 = ex2_fast(fmaf(__uint_as_float(sv[c][i]), scale_log2, -m_eff));
-          const float e1 = ex2_fast(fmaf(__uint_as_float(sv[c][i + 1]), scale_log2, -m_eff));
-          l4[(i >> 1) & 3] += e0 + e1;
-          packed[i >> 1] = pack_bf16x2(e0, e1);
-        }
-        unsigned char* prow = p_s + buf * TILE + (c >> 1) * SUB + row * 128;
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c & 1) * 4 + q4) ^ (row & 7);
-          *reinterpret_cast<uint4*>(prow + chunk * 16) =
-              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-        }
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = ex2_fast(fmaf(__uint_as_float(sv[2 * h2 + c][i]), scale_log2, -m_eff));
+            const float e1 = ex2_fast(fmaf(__uint_as_float(sv[2 * h2 + c][i + 1]), scale_log2, -m_eff));
+            l4[(i >> 1) & 3] += e0 + e1;
+            packed[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
+          }
+        tmem_st32(tmem_p + lane_addr + (uint32_t)(buf * 64 + h2 * 32), packed);
       }
+      tmem_st_wait();
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tc_fence_before();
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&p_full[buf]));
     }
@@ -399,7 +406,7 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
   if (rc) return rc;
   rc = tensor_map_2d_bf16(v_cache, cache_rows, HD, HD, 16, &mv);
   if (rc) return rc;
-  const size_t smem = 7 * (size_t)TILE + 1024;
+  const size_t smem = (1 + 2 * kStages) * (size_t)TILE + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
