@@ -7,10 +7,12 @@
 // position, and every CTA takes the same number of consecutive units whatever the lengths
 // of the requests are; a CTA's range may end in the middle of one pair and go on into the
 // next.  Roles by warp:
-//   warp 8, producer : walks the CTA's units and brings each tile's keys and values in with
-//                      TMA (cp.async.bulk.tensor.3d, boxes of 16 keys of the whole head at the
-//                      rows the block table names, 128-byte swizzle) into a ring of stages,
-//                      as far ahead as the ring is deep; it never waits for arithmetic.
+//   warps 8 and 9    : producers (keys; values).  Each walks the CTA's units and brings its
+//                      operand of every tile in with TMA (cp.async.bulk.tensor.3d, boxes of 16
+//                      keys of the whole head at the rows the block table names, 128-byte
+//                      swizzle) into a ring of stages, as far ahead as the ring is deep; they
+//                      never wait for arithmetic.  (Issuing a box costs a warp some 130
+//                      cycles whatever its size, hence two warps and boxes as big as a page.)
 //   warps 0-7        : two groups of four warps take tiles in turn.  A warp owns 16 keys of
 //                      its group's tile: Q.K^T and P.V on the tensor cores (mma.sync
 //                      m16n8k16, the query heads of the kv head padded to 16 rows), scores,
@@ -34,7 +36,7 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kThreads = kConsumers + 32;
+constexpr int kThreads = kConsumers + 64;          // two producer warps: keys, values
 constexpr int kTile = 64;                          // keys per unit
 constexpr int kMaxStages = 8;
 
@@ -77,7 +79,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
   constexpr uint32_t OPERAND = kTile * HD * 2;            // bytes of the keys (or the values) of one stage
   constexpr uint32_t STAGE = 2 * OPERAND;
   constexpr uint32_t BOX = 16 * HD * 2;                   // bytes of one box: 16 keys, as HD / 64 blocks of [16 x 128 bytes]
-  constexpr int NBOX = 2 * 4;                             // boxes of a stage: keys and values, 4 x 16 keys each
+  constexpr int NBOX = 4;                                 // boxes of an operand in a stage: 4 x 16 keys
   const int G = nq / nkv;
   const int C = (int)gridDim.x;
 
@@ -95,7 +97,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int i = 0; i < stages; ++i) {
-      mbar_init(smem_addr(&full[i]), 1);
+      mbar_init(smem_addr(&full[i]), 2);                  // the two producer warps, each with its bytes
       mbar_init(smem_addr(&empty[i]), 4);
     }
     abort_flag = 0;
@@ -104,8 +106,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
   // A warp reads a 16-key block of a stage only if the block has a key in range, and such a
   // block was loaded whole (slots of its page beyond the last key hold old, finite cache
   // contents that meet P = 0), so the ring needs no clearing.
-  if (warp == kConsumerWarps && lane < 2) {
-    const CUtensorMap* m = lane ? &map_v : &map_k;
+  if (warp >= kConsumerWarps && lane == 0) {
+    const CUtensorMap* m = warp > kConsumerWarps ? &map_v : &map_k;
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(m) : "memory");
   }
   for (int r = tid; r < R; r += kThreads) {
@@ -148,9 +150,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
   const volatile int* aborted = &abort_flag;
   const uint32_t ring_addr = smem_addr(ring);
 
-  if (warp == kConsumerWarps) {
+  if (warp >= kConsumerWarps) {
     // ------------------------------------------------------------------ producer
-    const int op = lane >> 2;                             // 0 keys, 1 values
+    const int op = warp - kConsumerWarps;                 // 0: this warp brings the keys, 1: the values
     const int c = lane & 3;                               // 16-key block of the tile
     const CUtensorMap* map = op ? &map_v : &map_k;
     const uint32_t dst_off = (uint32_t)op * OPERAND + (uint32_t)c * BOX;
