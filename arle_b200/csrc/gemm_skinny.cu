@@ -6,10 +6,14 @@
 //  * one CTA per SM (a persistent grid); the N weight rows are divided evenly among
 //    the CTAs to the row, not to a tile, so no SM gets a larger share;
 //  * weights travel global -> shared memory by the bulk async-copy engine
-//    (cp.async.bulk, one copy per weight-row segment, completion counted in bytes
-//    on an mbarrier), so the bytes in flight sit in shared memory rather than in
-//    registers: every warp keeps a ring of stages (16 weight rows x 256 or 128
-//    elements of K) filled ahead of its arithmetic;
+//    (cp.async.bulk, completion counted in bytes on an mbarrier), so the bytes in
+//    flight sit in shared memory rather than in registers.  Four producer warps keep
+//    a ring of stages filled ahead of the arithmetic; a stage is 16 weight rows x
+//    1,024 elements of K, one copy of 2 KB per row: issuing a copy costs a warp some
+//    150 cycles whatever its size, so rows of 512 bytes could not keep up with HBM
+//    (1.75 TB/s measured with 512-byte copies, 3.2 with 1 KB, 6.0 with 2 KB);
+//  * eight consumer warps share a stage, its blocks of 32 elements of K going round
+//    them;
 //  * x stays in shared memory for the whole launch;
 //  * the tensor cores do the arithmetic with W as the 16-row A operand and x^T as
 //    the B operand (mma.sync m16n8k16), float32 accumulators;
@@ -17,8 +21,7 @@
 //    cluster: each CTA of the cluster owns one K range (its slice of x and of every
 //    weight row) and rank 0 adds the partial sums through distributed shared
 //    memory, in rank order, so the result does not depend on timing;
-//  * the warps of a CTA take stages round-robin and their partial sums are added
-//    in warp order.
+//  * the consumer warps' partial sums are added in warp order.
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the kernel raises
 // the error flag and carries on to its end instead of hanging.
 //
@@ -33,8 +36,11 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
+constexpr int kConsumerWarps = 8;
+constexpr int kProducerWarps = 4;
+constexpr int kRowsPerProducer = 16 / kProducerWarps;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + kProducerWarps * 32;
 constexpr int kXPad = 8;                     // elements of padding per x row (16 bytes): rows fall on different banks
 constexpr int kRowPad = 16;                  // bytes of padding per weight-row segment of a stage
 constexpr int kPartTiles = 16;                // tiles whose partial sums a CTA of a cluster keeps for one reduction at the end
@@ -58,6 +64,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumers) : "memory"); }
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
@@ -67,26 +77,27 @@ template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-// NT: 8-row groups of x (1: M <= 8, 2: M <= 16).  KB: K elements per stage.  SLOTS: stages per warp.
-// KS: K elements owned by one CTA (K / cluster size, a multiple of 32).
-template <int NT, int KB, int SLOTS, typename OutT>
+// NT: 8-row groups of x (1: M <= 8, 2: M <= 16).  KS: K elements owned by one CTA (K / cluster
+// size, a multiple of 32).  KC: K elements per stage (a multiple of 32).  S: stages.
+template <int NT, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
     const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ W, int ldw, OutT* __restrict__ out,
-    int ldo, int M, int N, int K, int KS, int csize, int early, int gated, int* __restrict__ err) {
-  constexpr int PITCH = KB * 2 + kRowPad;                 // bytes per weight-row segment in a stage
-  constexpr int STAGE = 16 * PITCH;
+    int ldo, int M, int N, int K, int KS, int KC, int S, int csize, int early, int gated, int* __restrict__ err) {
+  const int pitch = KC * 2 + kRowPad;                     // bytes per weight row of a stage
+  const int stage_bytes = 16 * pitch;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int xrow = KS + kXPad;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                           // [NT*8][xrow]
   size_t off = ((size_t)NT * 8 * xrow * 2 + 127) / 128 * 128;
-  unsigned char* stages = smem_raw + off;                                                    // [kWarps][SLOTS][STAGE]
-  off += (size_t)kWarps * SLOTS * STAGE;
-  float* red = reinterpret_cast<float*>(smem_raw + off);                                     // [2][kWarps][16][NT*8]
-  off += (size_t)2 * kWarps * 16 * NT * 8 * sizeof(float);
+  unsigned char* stages = smem_raw + off;                                                    // [S][16][pitch]
+  off += (size_t)S * stage_bytes;
+  float* red = reinterpret_cast<float*>(smem_raw + off);                                     // [2][warps][16][NT*8]
+  off += (size_t)2 * kConsumerWarps * 16 * NT * 8 * sizeof(float);
   float* part = reinterpret_cast<float*>(smem_raw + off);                                    // [kPartTiles][16][NT*8] (clusters)
   off += (size_t)kPartTiles * 16 * NT * 8 * sizeof(float);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + off);                              // [kWarps][SLOTS], then x's
-  uint64_t* xbar = bars + kWarps * SLOTS;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + off);                              // [S], then empty [S], then x's
+  uint64_t* empty = full + S;
+  uint64_t* xbar = empty + S;
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -101,70 +112,98 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
   const int ks1 = min(K, ks0 + KS);
   const int klen = max(0, ks1 - ks0);
   const int tiles = (r1 - r0 + 15) / 16;
-  const int spt = (klen + KB - 1) / KB;                   // stages per 16-row tile
+  const int spt = (klen + KC - 1) / KC;                   // stages per 16-row tile
   const int total = tiles * spt;
   const bool batched = csize > 1 && tiles <= kPartTiles;    // few tiles: one cluster reduction at the end
 
-  if (lane == 0) {
-    for (int s = 0; s < SLOTS; ++s) mbar_init(smem_u32(&bars[warp * SLOTS + s]), 1);
-    if (warp == 0) mbar_init(smem_u32(xbar), 1);
-  }
-  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-  __syncwarp();
-  // this CTA's slice of x: one bulk copy per row (rows beyond M are zeroed by hand)
-  auto fetch_x = [&]() {
-    if (warp == 0 && klen > 0) {
-      if (lane == 0) mbar_expect_tx(smem_u32(xbar), (uint32_t)(min(M, NT * 8) * klen * 2));
-      __syncwarp();
-      if (lane < M && lane < NT * 8)
-        bulk_copy_g2s(smem_u32(xs + (size_t)lane * xrow), x + (size_t)lane * ldx + ks0, (uint32_t)(klen * 2), smem_u32(xbar));
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&full[s]), kProducerWarps);      // each producer warp arrives once, with its bytes
+      mbar_init(smem_u32(&empty[s]), kConsumerWarps);
     }
-  };
-  // x is the output of the kernel before this one.  Launched early (programmatic launch),
-  // the kernel fills its weight ring first (no kernel writes weights), then waits for that
-  // kernel, then fetches x; launched in stream order, x goes first because it is needed first.
-  if (!early) {
-    pdl_wait();
-    fetch_x();
+    mbar_init(smem_u32(xbar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
-
-  // stage number s of this CTA = (tile s / spt, K block s % spt); warp w owns s = w, w + kWarps, ...
-  auto issue = [&](int s, int slot) {
-    const int tile = s / spt, kb = s - tile * spt;
-    const int k0 = ks0 + kb * KB;
-    const int len = min(KB, ks1 - k0);
-    const int rt = r0 + tile * 16;
-    const int nvalid = min(16, r1 - rt);
-    const uint32_t bar = smem_u32(&bars[warp * SLOTS + slot]);
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(nvalid * len * 2));
-    __syncwarp();
-    if (lane < nvalid)
-      bulk_copy_g2s(smem_u32(stages + (size_t)(warp * SLOTS + slot) * STAGE + lane * PITCH),
-                    W + (size_t)(rt + lane) * ldw + k0, (uint32_t)(len * 2), bar);
-  };
-  int issued = 0;                                           // stages of this warp issued so far
-  for (; issued < SLOTS; ++issued) {
-    const int s = warp + issued * kWarps;
-    if (s < total) issue(s, issued);
-  }
-
-  if (early) {
-    pdl_wait();
-    fetch_x();
-  }
+  __syncthreads();
   bool timed_out = false;
+
+  if (warp >= kConsumerWarps) {
+    // ------------------------------------------------------------------ producers
+    // Warp p brings its four rows of every stage, one bulk copy per row (KC elements, 2 KB,
+    // contiguous in memory), as far ahead as the ring is deep.  (Issuing a copy costs a warp
+    // some 150 cycles whatever its size: hence long copies, issued from several warps.)
+    const int pw = warp - kConsumerWarps;
+    const int row = pw * kRowsPerProducer + lane;           // lanes 0 .. kRowsPerProducer - 1
+    // this CTA's slice of x: one bulk copy per row (rows beyond M are zeroed by the consumers)
+    auto fetch_x = [&]() {
+      if (pw == 0 && klen > 0) {
+        if (lane == 0) mbar_expect_tx(smem_u32(xbar), (uint32_t)(min(M, NT * 8) * klen * 2));
+        __syncwarp();
+        if (lane < M && lane < NT * 8)
+          bulk_copy_g2s(smem_u32(xs + (size_t)lane * xrow), x + (size_t)lane * ldx + ks0, (uint32_t)(klen * 2), smem_u32(xbar));
+      }
+    };
+    // x is the output of the kernel before this one.  Launched early (programmatic launch),
+    // the kernel fills its weight ring first (no kernel writes weights), then waits for that
+    // kernel, then fetches x; launched in stream order, x goes first because it is needed first.
+    if (!early) {
+      pdl_wait();
+      fetch_x();
+    }
+    int slot = 0;
+    uint32_t par = 0;
+    for (int s = 0; s < total; ++s) {
+      if (early && s == min(S, total)) {
+        pdl_wait();
+        fetch_x();
+      }
+      const int tile = s / spt, c = s - tile * spt;
+      const int k0 = ks0 + c * KC;
+      const int len = min(KC, ks1 - k0);
+      const int rt = r0 + tile * 16;
+      const int nvalid = min(16, r1 - rt);
+      const int mine = max(0, min(kRowsPerProducer, nvalid - pw * kRowsPerProducer));     // rows of this warp
+      if (lane == 0) {
+        if (!mbar_wait_bounded(smem_u32(&empty[slot]), par ^ 1)) timed_out = true;
+        mbar_expect_tx(smem_u32(&full[slot]), (uint32_t)(mine * len * 2));
+      }
+      __syncwarp();
+      if (lane < mine)
+        bulk_copy_g2s(smem_u32(stages + (size_t)slot * stage_bytes + (size_t)row * pitch), W + (size_t)(rt + row) * ldw + k0,
+                      (uint32_t)(len * 2), smem_u32(&full[slot]));
+      if (++slot == S) slot = 0, par ^= 1;
+    }
+    if (early && total <= S) {                              // fewer stages than the ring holds: x not fetched in the loop
+      pdl_wait();
+      fetch_x();
+    }
+    timed_out = __any_sync(0xffffffffu, timed_out);
+    if (csize > 1) {
+      // the cluster's barriers are for all threads: as many as the consumers pass
+      cg::cluster_group cluster = cg::this_cluster();
+      if (!batched)
+        for (int tile = 0; tile < tiles; ++tile) cluster.sync();
+      cluster.sync();
+      if (batched) cluster.sync();
+    }
+    if (timed_out && lane == 0 && err) atomicExch(err, 1);
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers
+  if (klen > 0 && !mbar_wait_bounded(smem_u32(xbar), 0)) timed_out = true;
   {
     const int per_row = klen / 8;
-    for (int i = tid; i < (NT * 8 - M) * per_row; i += kThreads) {
+    for (int i = tid; i < (NT * 8 - M) * per_row; i += kConsumers) {
       const int m = M + i / per_row, c = i % per_row;
       *reinterpret_cast<uint4*>(xs + (size_t)m * xrow + c * 8) = make_uint4(0, 0, 0, 0);
     }
   }
-  __syncthreads();                                          // zero rows written, x barrier initialised for all
-  if (klen > 0 && !mbar_wait_bounded(smem_u32(xbar), 0)) timed_out = true;
+  consumer_sync();                                          // zero rows written
 
-  int done = 0;                                             // stages of this warp consumed so far
+  int slot = 0;
+  uint32_t par = 0;
   for (int tile = 0; tile < tiles; ++tile) {
     // two accumulator sets, used by alternate K steps, halve the chain of dependent MMAs
     float acc[NT][4], acc2[NT][4];
@@ -173,20 +212,16 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
       acc2[n][0] = acc2[n][1] = acc2[n][2] = acc2[n][3] = 0.f;
     }
-    for (;;) {
-      const int s = warp + done * kWarps;
-      if (s >= total || s / spt != tile) break;
-      const int slot = done % SLOTS;
-      const uint32_t bar = smem_u32(&bars[warp * SLOTS + slot]);
-      if (!mbar_wait_bounded(bar, (uint32_t)((done / SLOTS) & 1))) timed_out = true;
-      const int kb = s - tile * spt;
-      const int kloc = kb * KB;                             // offset inside this CTA's K range
-      const int len = min(KB, klen - kloc);
-      const uint32_t st = smem_u32(stages + (size_t)(warp * SLOTS + slot) * STAGE);
-      const uint32_t a_addr = st + (lane & 15) * PITCH + (lane >> 4) * 16;
+    for (int c = 0; c < spt; ++c) {
+      if (!mbar_wait_bounded(smem_u32(&full[slot]), par)) timed_out = true;
+      const int kloc = c * KC;                              // offset inside this CTA's K range
+      const int len = min(KC, klen - kloc);
+      const uint32_t st = smem_u32(stages + (size_t)slot * stage_bytes);
+      const uint32_t a_addr = st + (lane & 15) * pitch + (lane >> 4) * 16;
       const __nv_bfloat16* xb = xs + (size_t)g * xrow + kloc + 2 * tq;
+      // the stage's blocks of 32 elements of K go round the warps
 #pragma unroll 2
-      for (int kk = 0; kk < len; kk += 32) {          // len is a multiple of 32
+      for (int kk = warp * 32; kk < len; kk += kConsumerWarps * 32) {
         uint32_t a[4], a2[4];
         ldsm_x4(a_addr + kk * 2, a[0], a[1], a[2], a[3]);
         ldsm_x4(a_addr + kk * 2 + 32, a2[0], a2[1], a2[2], a2[3]);
@@ -201,16 +236,11 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
         }
       }
       __syncwarp();
-      ++done;
-      const int nxt = warp + issued * kWarps;               // refill the slot just drained
-      if (nxt < total) {
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        issue(nxt, slot);
-      }
-      ++issued;
+      if (lane == 0) mbar_arrive(smem_u32(&empty[slot]));
+      if (++slot == S) slot = 0, par ^= 1;
     }
     // c0,c1: (weight row g, x rows 2t, 2t+1); c2,c3: (weight row g+8, same x rows)
-    float* rw = red + ((size_t)(tile & 1) * kWarps + warp) * 16 * NT * 8;
+    float* rw = red + ((size_t)(tile & 1) * kConsumerWarps + warp) * 16 * NT * 8;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
       rw[g * NT * 8 + n * 8 + 2 * tq] = acc[n][0] + acc2[n][0];
@@ -218,14 +248,14 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       rw[(g + 8) * NT * 8 + n * 8 + 2 * tq] = acc[n][2] + acc2[n][2];
       rw[(g + 8) * NT * 8 + n * 8 + 2 * tq + 1] = acc[n][3] + acc2[n][3];
     }
-    __syncthreads();
+    consumer_sync();
     const int rt = r0 + tile * 16;
     if (tid < 16 * NT * 8) {
       const int row = tid & 15, m = tid >> 4;
-      const float* rb = red + (size_t)(tile & 1) * kWarps * 16 * NT * 8 + row * NT * 8 + m;
+      const float* rb = red + (size_t)(tile & 1) * kConsumerWarps * 16 * NT * 8 + row * NT * 8 + m;
       float s = 0.f;
 #pragma unroll
-      for (int w = 0; w < kWarps; ++w) s += rb[(size_t)w * 16 * NT * 8];
+      for (int w = 0; w < kConsumerWarps; ++w) s += rb[(size_t)w * 16 * NT * 8];
       if (gated) {
         // rows 2i and 2i+1 of W are gate_i and up_i: out[m, i] = silu(gate) * up, in float32
         const float up = __shfl_down_sync(0xffffffffu, s, 1);
@@ -273,17 +303,36 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
   if (timed_out && err) atomicExch(err, 1);
 }
 
-template <int NT, int KB, int SLOTS>
-size_t smem_bytes(int KS) {
+template <int NT>
+size_t smem_bytes(int KS, int KC, int S) {
   size_t n = ((size_t)NT * 8 * (KS + kXPad) * 2 + 127) / 128 * 128;
-  n += (size_t)kWarps * SLOTS * 16 * (KB * 2 + kRowPad);
-  n += (size_t)2 * kWarps * 16 * NT * 8 * sizeof(float);
+  n += (size_t)S * 16 * (KC * 2 + kRowPad);
+  n += (size_t)2 * kConsumerWarps * 16 * NT * 8 * sizeof(float);
   n += (size_t)kPartTiles * 16 * NT * 8 * sizeof(float);
-  n += (size_t)(kWarps * SLOTS + 1) * sizeof(uint64_t);
+  n += (size_t)(2 * S + 1) * sizeof(uint64_t);
   return n;
 }
 
-template <int NT, int KB, int SLOTS, typename OutT>
+// The ring: stages of KC elements of K for 16 weight rows.  Long copies are what the copy engine
+// likes (a row of a stage is one copy of up to 2 KB), several stages keep enough bytes in flight.
+struct Ring {
+  int KC, S;
+};
+template <int NT>
+bool pick_ring(int KS, int max_smem, Ring* ring) {
+  const Ring tries[] = {{1024, 4}, {1024, 3}, {512, 4}, {256, 4}, {128, 4}, {64, 4}, {32, 4}};
+  for (const Ring& t : tries) {
+    Ring r = t;
+    if (r.KC > KS) r.KC = (KS + 31) / 32 * 32;            // a short K is one stage per tile
+    if (smem_bytes<NT>(KS, r.KC, r.S) <= (size_t)max_smem) {
+      *ring = r;
+      return true;
+    }
+  }
+  return false;
+}
+
+template <int NT, typename OutT>
 int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, int ldo, int M, int N, int K, int gated,
                     int* err, cudaStream_t s) {
   int dev = 0, sms = 0, max_smem = 0;
@@ -291,17 +340,19 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
   if (e != cudaSuccess) return (int)e;
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-  // the smallest cluster whose CTAs can each hold their slice of x
+  // the smallest cluster whose CTAs can each hold their slice of x beside a full-size ring
+  // (pairs of CTAs with three stages filled all SMs but measured no faster than triples with four)
+  const Ring want = {1024, 4};
   int csize = 1;
   int KS = K;
-  while (smem_bytes<NT, KB, SLOTS>(KS) > (size_t)max_smem) {
+  while (smem_bytes<NT>(KS, want.KC < KS ? want.KC : (KS + 31) / 32 * 32, want.S) > (size_t)max_smem) {
     ++csize;
     if (csize > 8) return ARLE_E_UNSUPPORTED;
     KS = ((K + csize - 1) / csize + 31) / 32 * 32;
   }
   if (gated && csize > 1) return ARLE_E_UNSUPPORTED;       // the gate needs whole sums in one CTA
-  auto kern = skinny_gemm_kernel<NT, KB, SLOTS, OutT>;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes<NT, KB, SLOTS>(KS));
+  auto kern = skinny_gemm_kernel<NT, OutT>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
   if (e != cudaSuccess) return (int)e;
   // A persistent grid must be resident at once: as many clusters as the GPU can hold together.
   // Clusters do not span GPCs, so one size may leave more SMs idle than the next: of the
@@ -315,7 +366,7 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(sms / c * c);
         cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = smem_bytes<NT, KB, SLOTS>(((K + c - 1) / c + 31) / 32 * 32);
+        cfg.dynamicSmemBytes = (size_t)max_smem - 1024;
         cfg.stream = s;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -336,13 +387,16 @@ int plan_and_launch(const void* x, int ldx, const void* W, int ldw, void* out, i
     KS = ((K + csize - 1) / csize + 31) / 32 * 32;
     groups = resident[csize] < sms / csize ? resident[csize] : sms / csize;
   }
-  const size_t smem = smem_bytes<NT, KB, SLOTS>(KS);
+  Ring ring;
+  if (!pick_ring<NT>(KS, max_smem, &ring)) return ARLE_E_UNSUPPORTED;
+  const size_t smem = smem_bytes<NT>(KS, ring.KC, ring.S);
   const int tiles = (N + 15) / 16;
   if (groups > tiles) groups = tiles;
   if (groups < 1) groups = 1;
   const bool early = (pdl_enabled() & 3) != 0;
   e = launch_kernel_as(early, kern, dim3(groups * csize), dim3(kThreads), smem, s, csize, (const __nv_bfloat16*)x, ldx,
-                       (const __nv_bfloat16*)W, ldw, (OutT*)out, ldo, M, N, K, KS, csize, early ? 1 : 0, gated, err);
+                       (const __nv_bfloat16*)W, ldw, (OutT*)out, ldo, M, N, K, KS, ring.KC, ring.S, csize, early ? 1 : 0,
+                       gated, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }
@@ -354,11 +408,11 @@ int skinny_entry(const void* x, int ldx, const void* W, int ldw, void* out, int 
   if (((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return ARLE_E_UNSUPPORTED;
   if (gated && N % 2 != 0) return ARLE_E_BADARG;
   if (M <= 8) {
-    if (out_dtype == 0) return plan_and_launch<1, 256, 2, float>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
-    if (out_dtype == 1) return plan_and_launch<1, 256, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
+    if (out_dtype == 0) return plan_and_launch<1, float>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
+    if (out_dtype == 1) return plan_and_launch<1, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
   } else {
-    if (out_dtype == 0) return plan_and_launch<2, 256, 2, float>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
-    if (out_dtype == 1) return plan_and_launch<2, 256, 2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
+    if (out_dtype == 0) return plan_and_launch<2, float>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
+    if (out_dtype == 1) return plan_and_launch<2, __nv_bfloat16>(x, ldx, W, ldw, out, ldo, M, N, K, gated, err, s);
   }
   return ARLE_E_BADARG;
 }
