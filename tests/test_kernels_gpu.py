@@ -421,6 +421,26 @@ def test_decode_attention_stream_kernel(nq, nkv, hd, ps, window, ctas):
         assert scratch[2].abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("ctas", [7, 148])
+def test_decode_attention_stream_many_rows(ctas):
+    """More rows than one warp scans at once, lengths of every kind, prompt rows in between."""
+    g = torch.Generator().manual_seed(11)
+    R = 77
+    lens = [int(v) for v in torch.randint(1, 400, (R,), generator=g)]
+    q_lens = [1] * R
+    for r in (3, 40, 41, 76):                      # rows of a prompt portion: left alone
+        q_lens[r] = min(lens[r], 5)
+    nq, nkv, hd, ps = 4, 2, 64, 16
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=12)
+    out = torch.full((q.shape[0], nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _stream_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, None, ctas)
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, None)
+    single = torch.tensor([int(qi[r]) for r in range(R) if q_lens[r] == 1])
+    multi = torch.tensor([t for r in range(R) if q_lens[r] > 1 for t in range(int(qi[r]), int(qi[r + 1]))])
+    assert out[multi.to(DEV)].isnan().all()
+    torch.testing.assert_close(out[single.to(DEV)].float().cpu(), exp[single], rtol=2e-2, atol=1e-2)
+
+
 def test_decode_attention_stream_skips_prompt_rows_and_stale_slots():
     """Rows with several queries are left alone, and cache slots beyond a request's last
     key, holding huge values, do not leak through P = 0."""
