@@ -340,7 +340,7 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
             prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
             prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
                     window, batch.max_q_len, skip_single=batch.num_single > 0)
-        if batch.num_single > 0 and stream_decode_supported(batch.num_rows, page_size):
+        if batch.num_single > 0 and stream_decode_supported(batch.num_rows, page_size, nq // nkv):
             ctas = sm_count(q.device)
             slots = (ctas + batch.num_rows * nkv) * (nq // nkv)
             paged_attention_decode_stream(
@@ -403,10 +403,13 @@ def sm_count(device) -> int:
     return _SM_COUNT[key]
 
 
-def stream_decode_supported(rows: int, page_size: int) -> bool:
+def stream_decode_supported(rows: int, page_size: int, group: int = 1) -> bool:
     """The streaming decode kernel fetches keys in TMA boxes of 16: pages must be
-    multiples of 16; its row table lives in shared memory: up to 2,048 rows."""
-    return page_size % 16 == 0 and rows <= 2048
+    multiples of 16; its row table lives in shared memory: up to 2,048 rows.  More than
+    4 query heads per kv head together with more than 8 rows is kept off it: 8 heads per
+    kv head at 64 rows (the Qwen3-32B sizes) ended in a launch failure whose cause reading
+    has not found, so that corner runs the split-KV kernel."""
+    return page_size % 16 == 0 and rows <= 2048 and (group <= 4 or rows <= 8)
 
 
 def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
@@ -423,6 +426,9 @@ def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, b
         raise KernelError("paged_attention_decode_stream: scratch for the pieces is missing or too small")
     if q.dtype != torch.bfloat16 or q.stride(1) != 1 or not out.is_contiguous():
         raise KernelError("paged_attention_decode_stream: needs bfloat16 queries with unit inner stride")
+    if not stream_decode_supported(R, page_size, nq // nkv):
+        raise KernelError(f"paged_attention_decode_stream: {R} rows with {nq // nkv} query heads per kv head and pages of "
+                          f"{page_size} are outside what this kernel is cleared for")
     _i32(q_indptr, "q_indptr"), _i32(kv_lens, "kv_lens"), _i32(block_table, "block_table")
     _check(library().arle_paged_attention_decode_stream(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(q_indptr), _ptr(kv_lens),

@@ -27,6 +27,12 @@ sys.path.insert(0, ROOT)
 QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
                 num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1e6,
                 rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu")
+# the other two sizes that BASELINE.json names, for runs beside the default one
+QWEN3_0_6B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+                  intermediate_size=3072, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
+                 intermediate_size=25600)
+SIZES = {"8b": QWEN3_8B, "0.6b": QWEN3_0_6B, "32b": QWEN3_32B}
 CONTEXT = 2048
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -98,6 +104,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than Qwen3-8B's 36 (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sizes", choices=sorted(SIZES), default="8b", help="layer sizes (default: Qwen3-8B, the contract's)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="profiling aid: run only the decode steps at --batch, or only the prefill")
     ap.add_argument("--no-cuda-graph", action="store_true")
@@ -129,8 +136,9 @@ def main() -> int:
     if args.tcgen05_gemm:
         ops.set_tcgen05_min_rows(128)
     pk = peaks()
-    layers = args.layers or QWEN3_8B["num_hidden_layers"]
-    model = random_model(QWEN3_8B, seed=0, dtype="bfloat16", device=dev, num_layers=layers)
+    sizes = SIZES[args.sizes]
+    layers = args.layers or sizes["num_hidden_layers"]
+    model = random_model(sizes, seed=0, dtype="bfloat16", device=dev, num_layers=layers)
     spec = model.spec
     vocab = spec.vocab_size
     page = 16
@@ -258,12 +266,13 @@ def main() -> int:
                "d2h_bytes_per_step": 4 * args.batch, "decoded_tokens": decoded}
 
     out = {
-        "metric": "decode tokens/s at batch 8, 2048-token context (Qwen3-8B sizes, bf16, one B200)",
+        "metric": f"decode tokens/s at batch {args.batch}, 2048-token context (Qwen3-{args.sizes.upper()} sizes, bf16, one B200)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded random weights, uniform random token ids, random cache contents)",
         "impl": "ours",
-        "config": {"model": "Qwen3-8B sizes, random weights", "layers": layers, "layers_of_config": 36,
+        "config": {"model": f"Qwen3-{args.sizes.upper()} sizes, random weights", "layers": layers,
+                   "layers_of_config": sizes["num_hidden_layers"],
                    "hidden_size": c.hidden_size, "num_attention_heads": c.num_attention_heads,
                    "num_key_value_heads": c.num_key_value_heads, "head_dim": c.head_dim,
                    "intermediate_size": c.intermediate_size, "vocab_size": vocab, "global_batch": args.batch,

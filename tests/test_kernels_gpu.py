@@ -467,6 +467,9 @@ def test_decode_attention_stream_refuses_small_pages():
     out = torch.zeros(1, 4 * 128, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(ops.KernelError):
         _stream_decode(q, out, kc, vc, qi, kv, bt, 4, 2, 128, 8, None, 8)
+    # and the corner it is not cleared for (many rows with many query heads per kv head)
+    assert ops.stream_decode_supported(64, 16, 4) and ops.stream_decode_supported(8, 16, 16)
+    assert not ops.stream_decode_supported(64, 16, 8) and not ops.stream_decode_supported(9, 16, 5)
 
 
 @pytest.mark.parametrize("nq,nkv,hd,ps,window", [(32, 8, 128, 16, None), (6, 1, 64, 8, None), (4, 4, 128, 16, 70),
