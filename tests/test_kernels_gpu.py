@@ -149,7 +149,7 @@ def test_gemm_skinny_weight_streaming(M, N, K, out_dtype):
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,I,K", [(1, 8, 32), (8, 12288, 4096), (3, 500, 192), (5, 37, 320), (8, 2050, 4096), (7, 100, 4608),
-                                   (9, 64, 64), (40, 176, 96), (2, 64, 8192)])
+                                   (9, 64, 64), (40, 176, 96), (2, 64, 8192), (8, 300, 5120), (4, 128, 5376)])
 def test_gemm_silu_mul(M, I, K, out_dtype):
     """Gate and up rows interleaved in one weight; few rows of x take the fused launch, more rows
     (or a K too long for one CTA) the product and the gate kernel: same numbers either way."""
