@@ -13,7 +13,7 @@ from arle_b200.engine import ModelRunner, load_model
 from tiny_models import CONFIGS, PAGE_SIZES, make_model_dir
 
 LENGTHS = {"A": [1, 5, 11, 23, 70, 130], "B": [2, 17, 40, 96, 67, 33], "C": [3, 50, 90, 120, 64, 35],
-           "D": [2, 65, 190, 128, 77, 40], "E": [1, 70, 129, 64, 300, 18]}
+           "D": [2, 65, 190, 128, 77, 40], "E": [1, 70, 129, 64, 300, 18], "F": [3, 66, 150, 64, 40, 97]}
 CUTS = ["whole", "tail_decode", "portions", "mixed"]
 # absolute tolerance on logits of magnitude ~1.5: float32 rounding through a few
 # layers; bfloat16 rounding of activations (8 mantissa bits) through the same.
@@ -63,7 +63,7 @@ def check(name, dtype, cut, device, tmp_path_factory, page_size=None):
 @pytest.mark.gpu
 @pytest.mark.parametrize("cut", CUTS)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_cuttings_gpu(name, dtype, cut, tmp_path_factory):
     check(name, dtype, cut, "cuda", tmp_path_factory)
 

@@ -136,7 +136,7 @@ def test_long_decoding(models):
     assert len(o.token_ids) == 300
 
 
-@pytest.mark.parametrize("name", ["D", "E"])
+@pytest.mark.parametrize("name", ["D", "E", "F"])
 def test_long_decoding_bf16_fast_kernels(name, tmp_path):
     """300 decoded tokens in bfloat16 on the configurations whose sizes reach the tensor-core
     attention and weight-streaming kernels: every emitted token must be (within bfloat16

@@ -32,11 +32,17 @@ TINY_E = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_si
               num_key_value_heads=1, head_dim=128, intermediate_size=320, vocab_size=1000, rope_theta=1000000.0,
               rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096, hidden_act="silu",
               bos_token_id=0, eos_token_id=1)
+# F is wider and deeper than the others (a width that is a multiple of 128, four layers, GQA 2, head 64).
+TINY_F = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=4, hidden_size=256, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=64, intermediate_size=416, vocab_size=777, rope_theta=300000.0,
+              rms_norm_eps=5e-6, tie_word_embeddings=True, max_position_embeddings=2048, hidden_act="silu",
+              bos_token_id=0, eos_token_id=2)
 INIT = {"A": dict(sigma=0.02, gain_jitter=0.1), "B": dict(sigma=0.03, gain_jitter=0.2),
         "C": dict(sigma=0.05, gain_jitter=0.15),
-        "D": dict(sigma=0.04, gain_jitter=0.1), "E": dict(sigma=0.03, gain_jitter=0.1)}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
-PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 16, "E": 16}
+        "D": dict(sigma=0.04, gain_jitter=0.1), "E": dict(sigma=0.03, gain_jitter=0.1),
+        "F": dict(sigma=0.03, gain_jitter=0.2)}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
+PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 16, "E": 16, "F": 16}
 
 
 def make_model_dir(name: str, seed: int = 0, root: str = None, **init) -> str:
