@@ -196,6 +196,26 @@ def test_random_model_is_seeded_and_order_free(tmp_path):
     assert json.load(open(os.path.join(a, "config.json"))) == CONFIGS["B"]
 
 
+def test_command_line_writes_a_random_model_folder(tmp_path):
+    """`python -m arle_b200 random-model`: a folder with config.json and model.safetensors that the
+    loader accepts, the same bytes as the library call with the same seed."""
+    import subprocess
+    import sys
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(CONFIGS["A"]))
+    out = tmp_path / "model"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "arle_b200", "random-model", "--config", str(cfg_path), "--seed", "5",
+                        "--sigma", "0.02", "--gain-jitter", "0.1", "--out", str(out)], capture_output=True, text=True, cwd=root)
+    assert r.returncode == 0, r.stderr
+    ref = make_model_dir("A", seed=5, root=str(tmp_path / "lib"))
+    fa, fb = SafetensorsFile(str(out / "model.safetensors")), SafetensorsFile(os.path.join(ref, "model.safetensors"))
+    assert sorted(fa.names()) == sorted(fb.names())
+    for n in fa.names():
+        assert torch.equal(fa.tensor(n), fb.tensor(n))
+    assert json.load(open(out / "config.json")) == CONFIGS["A"]
+
+
 def test_model_build_maps_cache_layers_and_groups():
     m = DecoderModel(config_from_dict(TINY_C).to_model_spec())
     assert m.entry_cache_layer == [0, 1, 2, 3] and [n.window for n in m.cache_needs] == [None, None, 21, 21]
