@@ -39,6 +39,7 @@ constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 64;          // two producer warps: keys, values
 constexpr int kTile = 64;                          // keys per unit
 constexpr int kMaxStages = 8;
+constexpr int kStaticSmem = 2 * kMaxStages * 8 + 16;   // bytes of __shared__ variables in the kernel: the barriers, two flags
 
 __device__ __forceinline__ void mbar_arrive_one(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
@@ -212,8 +213,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
       }
       u = pe;
     }
-    // after a wait ran out: let the copies that are still in flight land before the CTA ends
-    if (*aborted && lane == 0) {
+    // No copy may still be in flight when the CTA ends.  The consumers have waited for every tile
+    // unless a wait ran out, so this is free otherwise.
+    if (lane == 0) {
       for (int s = 0; s < stages && s < issued; ++s) {
         const int last = (issued - 1 - s) / stages * stages + s;       // last tile issued into stage s
         mbar_wait_plain(smem_addr(&full[s]), (uint32_t)((last / stages) & 1));
@@ -442,7 +444,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
 }
 
 size_t fixed_smem(int G, int hd, int ctas, int R) {
-  size_t n = (size_t)kConsumerWarps * G * hd * 4 + (size_t)kConsumerWarps * 16 * 2 * 4 + 64;
+  size_t n = (size_t)kConsumerWarps * G * hd * 4 + (size_t)kConsumerWarps * 16 * 2 * 4;
   n += (size_t)(3 * R + 1) * 4;
   return (n + 15) / 16 * 16;
 }
@@ -460,12 +462,20 @@ int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, i
   if (e != cudaSuccess) return (int)e;
   cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   const size_t stage = (size_t)2 * kTile * HD * 2;
-  const size_t fixed = fixed_smem(nq / nkv, HD, ctas, rows) + 1024 + 256;      // alignment slack, static shared memory
-  if (fixed + 3 * stage > (size_t)max_smem) return ARLE_E_UNSUPPORTED;
+  const size_t fixed = fixed_smem(nq / nkv, HD, ctas, rows) + 1024 + kStaticSmem;      // alignment slack, static shared memory
+  if (fixed + 2 * stage > (size_t)max_smem) return ARLE_E_UNSUPPORTED;
+  // The ring's depth is even.  The two consumer groups take alternate tiles, so with an even depth a
+  // stage always serves the same group, whose waits on it alternate in parity.  With an odd depth a
+  // stage serves the groups in turn and each group waits on it with the same parity every time: a
+  // group that comes back to a stage while the other group's load into it has not landed yet (copies
+  // issued later may land earlier) would find the phase of its parity complete, read the stage as it
+  // is and release it a phase early, and from there on copies overwrite stages in use and may still
+  // be in flight when the CTA ends.
   int stages = (int)(((size_t)max_smem - fixed) / stage);
   if (stages > kMaxStages) stages = kMaxStages;
-  const size_t smem = fixed - 256 + (size_t)stages * stage;
-  e = cudaFuncSetAttribute(decode_stream_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - 256);
+  stages &= ~1;
+  const size_t smem = fixed - kStaticSmem + (size_t)stages * stage;
+  e = cudaFuncSetAttribute(decode_stream_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - kStaticSmem);
   if (e != cudaSuccess) return (int)e;
   e = launch_kernel(decode_stream_kernel<HD>, dim3(ctas), dim3(kThreads), smem, s, 1, mk, mv, (const __nv_bfloat16*)q,
                     q_row_stride, (__nv_bfloat16*)out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,

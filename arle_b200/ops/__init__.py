@@ -405,11 +405,9 @@ def sm_count(device) -> int:
 
 def stream_decode_supported(rows: int, page_size: int, group: int = 1) -> bool:
     """The streaming decode kernel fetches keys in TMA boxes of 16: pages must be
-    multiples of 16; its row table lives in shared memory: up to 2,048 rows.  More than
-    4 query heads per kv head together with more than 8 rows is kept off it: 8 heads per
-    kv head at 64 rows (the Qwen3-32B sizes) ended in a launch failure whose cause reading
-    has not found, so that corner runs the split-KV kernel."""
-    return page_size % 16 == 0 and rows <= 2048 and (group <= 4 or rows <= 8)
+    multiples of 16; its row table lives in shared memory: up to 2,048 rows; the query
+    heads of a kv head are the 16 rows of one MMA."""
+    return page_size % 16 == 0 and rows <= 2048 and group <= 16
 
 
 def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, block_table, nq, nkv, hd, page_size, scale,
@@ -428,7 +426,7 @@ def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, b
         raise KernelError("paged_attention_decode_stream: needs bfloat16 queries with unit inner stride")
     if not stream_decode_supported(R, page_size, nq // nkv):
         raise KernelError(f"paged_attention_decode_stream: {R} rows with {nq // nkv} query heads per kv head and pages of "
-                          f"{page_size} are outside what this kernel is cleared for")
+                          f"{page_size} are outside what this kernel takes")
     _i32(q_indptr, "q_indptr"), _i32(kv_lens, "kv_lens"), _i32(block_table, "block_table")
     _check(library().arle_paged_attention_decode_stream(
         _ptr(q), q.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(q_indptr), _ptr(kv_lens),

@@ -467,9 +467,26 @@ def test_decode_attention_stream_refuses_small_pages():
     out = torch.zeros(1, 4 * 128, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(ops.KernelError):
         _stream_decode(q, out, kc, vc, qi, kv, bt, 4, 2, 128, 8, None, 8)
-    # and the corner it is not cleared for (many rows with many query heads per kv head)
-    assert ops.stream_decode_supported(64, 16, 4) and ops.stream_decode_supported(8, 16, 16)
-    assert not ops.stream_decode_supported(64, 16, 8) and not ops.stream_decode_supported(9, 16, 5)
+    assert ops.stream_decode_supported(64, 16, 8) and not ops.stream_decode_supported(64, 16, 17)
+
+
+@pytest.mark.parametrize("nq,nkv,hd,R,n", [(64, 8, 128, 64, 2048), (16, 1, 128, 64, 2048), (32, 8, 128, 40, 3000),
+                                           (14, 2, 64, 64, 1500)])
+def test_decode_attention_stream_long_runs(nq, nkv, hd, R, n):
+    """Many rows of long contexts: every CTA walks a hundred tiles and more, across several pairs,
+    with HBM saturated, so that copies land far out of the order they were issued in.  The ring's
+    depth (which the shared memory left beside the merge scratch decides, and which must be even for
+    the two consumer groups' waits to tell a stage's phases apart) differs between these shapes."""
+    ps = 16
+    lens = [n - (r % 5) * 13 for r in range(R)]
+    q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, [1] * R, seed=21)
+    exp = _ref_attn(q, kc, vc, pos, rows, bt, nq, nkv, hd, ps, None)
+    out = torch.zeros(R, nq * hd, dtype=torch.bfloat16, device=DEV)
+    scratch = None
+    for _ in range(3):
+        out.zero_()
+        scratch = _stream_decode(q, out, kc, vc, qi, kv, bt, nq, nkv, hd, ps, None, 148, scratch)
+        torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
 
 
 @pytest.mark.parametrize("nq,nkv,hd,ps,window", [(32, 8, 128, 16, None), (6, 1, 64, 8, None), (4, 4, 128, 16, 70),
