@@ -39,7 +39,7 @@ constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + 64;          // two producer warps: keys, values
 constexpr int kTile = 64;                          // keys per unit
 constexpr int kMaxStages = 8;
-constexpr int kStaticSmem = 2 * kMaxStages * 8 + 16;   // bytes of __shared__ variables in the kernel: the barriers, two flags
+constexpr int kStaticSmem = 2 * kMaxStages * 8 + 32;   // bytes of __shared__ variables in the kernel: the barriers, six words
 
 __device__ __forceinline__ void mbar_arrive_one(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
   int* tok = kvl + R;                                                       // [R]
   __shared__ __align__(8) uint64_t full[kMaxStages], empty[kMaxStages];
   __shared__ int abort_flag, is_last;
+  __shared__ int own_row, own_first, own_k, by_pair;        // the CTA's place when pairs are shared out whole (below)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
@@ -144,8 +145,52 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
 
   const int U = prefix[R];
   const int per = max(1, (U + C - 1) / C);               // units per CTA
-  const int u0 = (int)blockIdx.x * per;
-  const int u1 = min(U, u0 + per);
+  // Two ways of sharing out the units.  Evenly, whatever the pairs are: CTA c takes units
+  // [c * per, (c + 1) * per), and its range may end inside one pair and go on into the next; every such
+  // piece costs a merge and a hand-over.  Or, when there are fewer pairs than CTAs (few rows), by pair:
+  // the pairs of row r get k_r = T_r C / U CTAs each (T_r tiles, rounded down, at least one) and a CTA takes
+  // one piece of one pair, ceil(T_r / k_r) tiles: one merge per CTA, and none handed over when k_r = 1.
+  // By pair is taken when no CTA gets more than 5/4 of an even share.
+  if (warp == 0) {
+    int mine_row = -1, mine_first = 0, mine_k = 0, carry = 0, worst = 0;
+    const bool may = U > 0 && (long long)R * nkv <= C;
+    for (int base = 0; may && base < R; base += 32) {
+      const int i = base + lane;
+      const int T_i = i < R ? (prefix[i + 1] - prefix[i]) / nkv : 0;
+      const int k_i = T_i > 0 ? max(1, (int)((long long)T_i * C / U)) : 0;
+      worst = max(worst, k_i ? (T_i + k_i - 1) / k_i : 0);
+      int v = k_i * nkv;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      const int first = carry + v - k_i * nkv;
+      if (k_i && first <= (int)blockIdx.x && (int)blockIdx.x < first + k_i * nkv) mine_row = i, mine_first = first, mine_k = k_i;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) worst = max(worst, __shfl_xor_sync(0xffffffffu, worst, o));
+    const bool take = may && carry <= C && 4 * worst <= 5 * per;
+    if (lane == 0) by_pair = take ? 1 : 0, own_row = -1;
+    __syncwarp();
+    if (take && mine_row >= 0) own_row = mine_row, own_first = mine_first, own_k = mine_k;
+  }
+  __syncthreads();
+  int u0, u1;
+  if (by_pair) {
+    if (own_row < 0) return;
+    const int T = (prefix[own_row + 1] - prefix[own_row]) / nkv;
+    const int rel = (int)blockIdx.x - own_first;
+    const int kvh = rel / own_k, piece = rel - kvh * own_k;
+    const int tp = (T + own_k - 1) / own_k;
+    const int pair_begin = prefix[own_row] + kvh * T;
+    u0 = pair_begin + piece * tp;
+    u1 = min(pair_begin + T, u0 + tp);
+  } else {
+    u0 = (int)blockIdx.x * per;
+    u1 = min(U, u0 + per);
+  }
   if (u0 >= u1) return;
   const Rows rows{prefix, kvl, R, nkv, window};
   const volatile int* aborted = &abort_flag;
@@ -366,9 +411,20 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
       }
       consumer_sync();
       const int pidx = r * nkv + kvh;
-      const int first_cta = pair_begin / per, last_cta = (pair_begin + T - 1) / per;
-      const int pieces = last_cta - first_cta + 1;
-      const int slot = (int)blockIdx.x + pidx;                // pieces of a pair lie side by side: first_cta + pidx ...
+      // pieces of a pair lie side by side in the scratch: from slot first_cta + pidx when the units are shared
+      // out evenly (a CTA index alone would repeat where a CTA holds pieces of two pairs), from the pair's first
+      // CTA when they are shared out by pair
+      int first_cta, pieces, slot;
+      if (by_pair) {
+        const int tp = (T + own_k - 1) / own_k;
+        first_cta = own_first + kvh * own_k;                  // the pair's first CTA; a piece's slot is its CTA
+        pieces = (T + tp - 1) / tp;                           // pieces that have tiles
+        slot = (int)blockIdx.x;
+      } else {
+        first_cta = pair_begin / per + pidx;
+        pieces = (pair_begin + T - 1) / per - pair_begin / per + 1;
+        slot = (int)blockIdx.x + pidx;
+      }
       for (int i = tid; i < G * HD; i += kConsumers) {
         const int row = i / HD, d = i % HD;
         float M = mm[row];
@@ -405,7 +461,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
         consumer_sync();
         if (is_last) {
           __threadfence();
-          const size_t base = (size_t)(first_cta + pidx) * G;
+          const size_t base = (size_t)first_cta * G;
           for (int i = tid; i < G * HD / 2; i += kConsumers) {
             const int row = i / (HD / 2), d = (i % (HD / 2)) * 2;
             const float2* po = reinterpret_cast<const float2*>(part_o + (base + row) * HD + d);
