@@ -1,36 +1,42 @@
 // Paged causal attention for prompt portions on the fifth-generation tensor cores
 // (tcgen05), head size 128, bfloat16, page sizes that are multiples of 16.
 //
-// One CTA serves 128 consecutive queries of one request and one query head and walks
-// the visible keys in tiles of 128 (boundaries at multiples of 128 of the absolute key
-// position).  Everything big lives where the tensor cores want it:
-//   shared memory : Q (128 x 128) and three stages each of K and V (128 keys x 128), in the
-//                   128-byte swizzled layout that TMA writes and tcgen05.mma reads;
-//   tensor memory : two buffers for the scores S (128 lanes x 128 columns, float32), the
-//                   output accumulator O (128 x 128, float32) and two buffers for P
-//                   (128 lanes x 64 columns, two bfloat16 per column): all 512 columns.
-// Roles by warp:
-//   warps 4 and 6    : loaders (keys; values).  TMA tile loads (cp.async.bulk.tensor.2d): Q
-//                      once from the packed projection output, then per tile the keys or the
-//                      values page by page (16 keys x 64 elements per box, one box per lane)
-//                      at the rows the block table names.
-//   warp 5, one lane : MMA issuer.  S(j) = Q . K(j)^T (eight tcgen05.mma of K 16, both operands
-//                      K-major) into S buffer j mod 2, one tile ahead of the softmax;
-//                      O += P(j) . V(j) (eight tcgen05.mma with P as the A operand read from
-//                      tensor memory, and V used as it lies in the cache: an MN-major B
-//                      operand).  tcgen05.commit signals the mbarriers.
-//   warps 0-3        : softmax and epilogue; thread i owns query row i (TMEM lane i), so row
-//                      maxima and sums need no shuffles.  A thread reads its row of S into
-//                      registers, masks (key <= query position, and > position - window)
-//                      and finds the row maximum; O and the running sum are rescaled only
-//                      when the maximum grew by more than 2^8 since the last rescale (the
-//                      exponentials stay within float32 and bfloat16 range); then it
-//                      exponentiates, adds up and writes P as bfloat16 into tensor memory
-//                      (tcgen05.st, two buffers), as cklxx/arle's prefill kernel rounds P
+// One CTA serves 256 consecutive queries of one request and one query head as two query
+// tiles of 128 (A: the first 128 rows, B: the next) and walks the visible keys in tiles of
+// 128 (boundaries at multiples of 128 of the absolute key position).  The two tiles share
+// every key and value tile the CTA loads, and while the softmax of one runs the tensor core
+// works for the other.  Everything big lives where the tensor cores want it:
+//   shared memory : Q of both tiles (2 x 128 x 128) and two stages each of K and V (128 keys x
+//                   128), in the 128-byte swizzled layout that TMA writes and tcgen05.mma reads;
+//   tensor memory : the scores S of tile A and of tile B (128 lanes x 128 columns, float32
+//                   each) and the output accumulators O of A and of B (128 x 128, float32):
+//                   all 512 columns.  P of a tile is written, as bfloat16 pairs, over the first
+//                   64 columns of its S once the row of S is in registers.
+// Roles by warp (three warp groups; the first two take registers from the third with setmaxnreg):
+//   warps 0-3, 4-7   : softmax and epilogue of tile A and of tile B; thread i owns query row i
+//                      (TMEM lane i), so row maxima and sums need no shuffles.  A thread reads
+//                      its row of S into registers, masks (key <= query position, and >
+//                      position - window) and finds the row maximum; O and the running sum are
+//                      rescaled only when the maximum grew by more than 2^8 since the last
+//                      rescale (the exponentials stay within float32 and bfloat16 range); then
+//                      it exponentiates, adds up and writes P into tensor memory (tcgen05.st),
+//                      rounded to bfloat16 as cklxx/arle's prefill kernel rounds P
 //                      (crates/cuda-kernels/tools/tilelang/batch_prefill_paged_hd128.py:223-225).
 //                      After the last tile the rows are divided by their sums and stored.
-// Scores, maxima, sums and the accumulator are float32.  Every mbarrier wait is bounded;
-// when one runs out the kernel raises the error flag, stops, frees its TMEM and returns.
+//   warp 8, one lane : MMA issuer.  Per key tile j and query tile x: O_x += P_x(j) . V(j) (eight
+//                      tcgen05.mma with P as the A operand read from tensor memory, and V used
+//                      as it lies in the cache: an MN-major B operand), then S_x(j + 1) = Q_x .
+//                      K(j + 1)^T (eight tcgen05.mma of K 16, both operands K-major) over the P
+//                      just used: the tensor core runs one thread's instructions in order.
+//                      tcgen05.commit signals the mbarriers; since a commit covers everything
+//                      issued before it, "S_x(j + 1) is ready" also says that P_x(j) . V(j) is
+//                      done, so the softmax may rescale O_x without a further wait.
+//   warps 9 and 10   : loaders (keys and Q; values).  TMA tile loads (cp.async.bulk.tensor.2d):
+//                      per tile the keys or the values page by page (16 keys x 64 elements per
+//                      box, one box per lane) at the rows the block table names.
+// Blocks are handed out heaviest first (the last queries of all heads before any earlier
+// block).  Scores, maxima, sums and the accumulators are float32.  Every mbarrier wait is
+// bounded; when one runs out the kernel raises the error flag, stops, frees its TMEM and returns.
 #include "common.cuh"
 #include "tcgen05_utils.cuh"
 using namespace arle;
@@ -38,12 +44,15 @@ using namespace arle;
 namespace {
 
 constexpr int HD = 128;
-constexpr int BQ = 128;                      // queries per CTA
+constexpr int BQ = 128;                      // queries per query tile
+constexpr int BQ2 = 2 * BQ;                  // queries per CTA: two query tiles
 constexpr int BKV = 128;                     // keys per tile
-constexpr int kThreads = 224;
+constexpr int kThreads = 384;                // three warp groups: softmax of tile A, softmax of tile B, the rest
+constexpr int kMmaWarp = 8, kKeyWarp = 9, kValueWarp = 10;
+constexpr int kRegsSoftmax = 208, kRegsOther = 80;   // registers per thread after the warp groups have traded
 constexpr uint32_t SUB = 128 * 128;          // bytes of a [128 rows x 64 elements] swizzled sub-tile
 constexpr uint32_t TILE = 2 * SUB;           // 128 x 128 bfloat16
-constexpr int kStages = 3;                   // stages of keys and of values
+constexpr int kStages = 2;                   // stages of keys and of values
 constexpr float kRescaleStep = 8.0f;         // log2 units the maximum may grow before O is rescaled
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -85,6 +94,11 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr, uint32_t l
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
+template <int N>
+__device__ __forceinline__ void reg_more() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_less() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(N)); }
+
 __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, const int* __restrict__ q_indptr,
@@ -92,28 +106,46 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     int page_size, float scale_log2, int window, int skip_single, int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.z, h = blockIdx.y;
+  const int r = blockIdx.z, h = blockIdx.x;
   const int t0 = q_indptr[r];
   const int qlen = q_indptr[r + 1] - t0;
-  // the blocks with the most keys (the last queries) are scheduled first
-  const int mbeg = (int)(gridDim.x - 1 - blockIdx.x) * BQ;
+  // The blocks with the most keys (the last queries) are scheduled first, for all heads before any
+  // block with fewer: blocks are handed out with x running fastest, and a long block that starts
+  // late is what the others would wait for at the end.
+  const int mbeg = (int)(gridDim.y - 1 - blockIdx.y) * BQ2;
   if (mbeg >= qlen || (skip_single && qlen == 1)) return;
   const int kv_len = kv_lens[r];
   const int pos0 = kv_len - qlen;
-  const int rows_here = min(BQ, qlen - mbeg);
-  const int p_first = pos0 + mbeg, p_last = pos0 + mbeg + rows_here - 1;
-  const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
-  const int kb = lo / BKV * BKV;
-  const int ntiles = (p_last - kb) / BKV + 1;
   const int kvh = h / (nq / nkv);
+  // The two query tiles: rows, positions of the first and last row, first key, tiles [jlo, jhi) of
+  // the CTA's sequence of key tiles (which starts at kb, a multiple of 128).
+  int rows_x[2], pf_x[2], pl_x[2], lo_x[2], jlo_x[2], jhi_x[2];
+  rows_x[0] = min(BQ, qlen - mbeg);
+  rows_x[1] = max(0, min(BQ, qlen - mbeg - BQ));
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    pf_x[x] = pos0 + mbeg + x * BQ;
+    pl_x[x] = pf_x[x] + max(rows_x[x], 1) - 1;
+    lo_x[x] = (window > 0 && pf_x[x] - window + 1 > 0) ? pf_x[x] - window + 1 : 0;
+  }
+  const int kb = lo_x[0] / BKV * BKV;
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    jlo_x[x] = (lo_x[x] / BKV * BKV - kb) / BKV;
+    jhi_x[x] = rows_x[x] > 0 ? (pl_x[x] - kb) / BKV + 1 : 0;
+    if (rows_x[x] == 0) jlo_x[x] = 0;
+  }
+  const int ntiles = max(jhi_x[0], jhi_x[1]);
+  const int lo = lo_x[0];                                  // first key any row of the CTA sees
+  const int p_last = rows_x[1] > 0 ? pl_x[1] : pl_x[0];    // last key any row of the CTA sees
 
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_s = base;                      // TILE
-  unsigned char* k_s = base + TILE;                       // kStages x TILE
-  unsigned char* v_s = base + (1 + kStages) * TILE;       // kStages x TILE
-  __shared__ __align__(8) uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], s_empty[2], p_full[2],
-      pv_done[2];
+  unsigned char* q_s = base;                              // 2 x TILE
+  unsigned char* k_s = base + 2 * TILE;                   // kStages x TILE
+  unsigned char* v_s = base + (2 + kStages) * TILE;       // kStages x TILE
+  __shared__ __align__(8) uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_full[2], p_full[2],
+      o_full[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -128,12 +160,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_addr(&s_full[i]), 1);
-      mbar_init(smem_addr(&s_empty[i]), 4);
+      mbar_init(smem_addr(&p_full[i]), 4);
+      mbar_init(smem_addr(&o_full[i]), 1);
     }
-    mbar_init(smem_addr(&p_full[0]), 4);
-    mbar_init(smem_addr(&p_full[1]), 4);
-    mbar_init(smem_addr(&pv_done[0]), 1);
-    mbar_init(smem_addr(&pv_done[1]), 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -141,7 +170,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   // numbers, not whatever bits shared memory had.
   for (uint32_t i = threadIdx.x; i < kStages * TILE / 16; i += kThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_addr(&tmem_base_slot), 512);
     tmem_relinquish();
   }
@@ -149,128 +178,158 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tmem_o = tmem_base + 256;
-  const uint32_t tmem_p = tmem_base + 384;                    // two buffers of 64 columns: P as packed bfloat16 pairs
+  // columns: S of tile A, S of tile B, O of tile A, O of tile B (128 each).  P of a tile is written over
+  // the first 64 columns of its S (two bfloat16 a column) once the row of S is in registers.
   const volatile int* aborted = &abort_flag;
 
-  if (warp == 4 || warp == 6) {
-    // Warp 4 loads the keys, warp 6 the values, each at its own pace: a tile is 16 boxes per
-    // operand (8 pages x 2 halves of the head), one per lane, so that their issue overlaps;
-    // lane 0 waits for the stage and arms its barrier.  A key stage frees as soon as S of two
-    // tiles ago is computed, a value stage only after P.V of two tiles ago.
-    const bool keys = warp == 4;
-    if (keys && lane == 0) {
-      mbar_expect_tx(smem_addr(&q_full), TILE);
-      tma_load_2d(smem_addr(q_s), &map_q, h * HD, t0 + mbeg, smem_addr(&q_full));
-      tma_load_2d(smem_addr(q_s + SUB), &map_q, h * HD + 64, t0 + mbeg, smem_addr(&q_full));
-    }
-    const int* bt = block_table + (size_t)r * bt_stride;
-    const int c = (lane >> 1) & 7, half = lane & 1;      // page of the tile, half of the head (lanes 0..15)
-    const CUtensorMap* map = keys ? &map_k : &map_v;
-    unsigned char* tile_s = keys ? k_s : v_s;
-    // Page ids come 32 at a time, one per lane, with the next 32 already in flight, so that no
-    // tile waits for a read of the block table; a lane picks its page with a shuffle.
-    int p0 = kb / page_size;
-    int cur = __ldg(bt + min(p0 + lane, bt_width - 1));
-    int nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
-    for (int j = 0; j < ntiles; ++j) {
-      const int st = j % kStages;
-      const uint32_t par = (uint32_t)((j / kStages) & 1);
-      const int key0 = kb + j * BKV + c * 16;
-      while ((kb + j * BKV) / page_size - p0 >= 32) {
-        cur = nxt;
-        p0 += 32;
-        nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
-      }
-      const int pi = key0 / page_size;
-      const int rel = pi - p0;                                // 0 .. 63: a tile spans at most 8 pages
-      const int from_cur = __shfl_sync(0xffffffffu, cur, rel & 31), from_nxt = __shfl_sync(0xffffffffu, nxt, rel & 31);
-      int row = -1;
-      if (lane < 16 && key0 <= p_last && key0 + 15 >= lo) {
-        const int page = rel < 32 ? from_cur : from_nxt;
-        row = (page * nkv + kvh) * page_size + (key0 - pi * page_size);
-      }
-      const int n = __popc(__ballot_sync(0xffffffffu, row >= 0)) >> 1;      // pages of this tile
-      uint64_t* full = keys ? &k_full[st] : &v_full[st];
-      int go = 1;
-      if (lane == 0) {
-        if (!mbar_wait_bounded(smem_addr(keys ? &k_empty[st] : &v_empty[st]), par ^ 1, aborted)) {
-          abort_flag = 1;
-          go = 0;
-        } else {
-          mbar_expect_tx(smem_addr(full), (uint32_t)n * 4096u);
+  if (warp >= 8) {
+    reg_less<kRegsOther>();
+    if (warp == kKeyWarp || warp == kValueWarp) {
+      // One warp loads the keys, one the values, each at its own pace: a tile is 16 boxes per
+      // operand (8 pages x 2 halves of the head), one per lane, so that their issue overlaps;
+      // lane 0 waits for the stage and arms its barrier.
+      const bool keys = warp == kKeyWarp;
+      if (keys && lane == 0) {
+        const int nload = rows_x[1] > 0 ? 2 : 1;
+        mbar_expect_tx(smem_addr(&q_full), (uint32_t)nload * TILE);
+        for (int x = 0; x < nload; ++x) {
+          tma_load_2d(smem_addr(q_s + x * TILE), &map_q, h * HD, t0 + mbeg + x * BQ, smem_addr(&q_full));
+          tma_load_2d(smem_addr(q_s + x * TILE + SUB), &map_q, h * HD + 64, t0 + mbeg + x * BQ, smem_addr(&q_full));
         }
       }
-      go = __shfl_sync(0xffffffffu, go, 0);
-      if (!go || *aborted) break;
-      if (row >= 0) tma_load_2d(smem_addr(tile_s + st * TILE + half * SUB + c * 2048), map, half * 64, row, smem_addr(full));
-    }
-  } else if (warp == 5) {
-    if (lane == 0) {
+      const int* bt = block_table + (size_t)r * bt_stride;
+      const int c = (lane >> 1) & 7, half = lane & 1;      // page of the tile, half of the head (lanes 0..15)
+      const CUtensorMap* map = keys ? &map_k : &map_v;
+      unsigned char* tile_s = keys ? k_s : v_s;
+      // Page ids come 32 at a time, one per lane, with the next 32 already in flight, so that no
+      // tile waits for a read of the block table; a lane picks its page with a shuffle.
+      int p0 = kb / page_size;
+      int cur = __ldg(bt + min(p0 + lane, bt_width - 1));
+      int nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
+      for (int j = 0; j < ntiles; ++j) {
+        const int st = j % kStages;
+        const uint32_t par = (uint32_t)((j / kStages) & 1);
+        const int key0 = kb + j * BKV + c * 16;
+        while ((kb + j * BKV) / page_size - p0 >= 32) {
+          cur = nxt;
+          p0 += 32;
+          nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
+        }
+        const int pi = key0 / page_size;
+        const int rel = pi - p0;                                // 0 .. 63: a tile spans at most 8 pages
+        const int from_cur = __shfl_sync(0xffffffffu, cur, rel & 31), from_nxt = __shfl_sync(0xffffffffu, nxt, rel & 31);
+        int row = -1;
+        if (lane < 16 && key0 <= p_last && key0 + 15 >= lo) {
+          const int page = rel < 32 ? from_cur : from_nxt;
+          row = (page * nkv + kvh) * page_size + (key0 - pi * page_size);
+        }
+        const int n = __popc(__ballot_sync(0xffffffffu, row >= 0)) >> 1;      // pages of this tile
+        uint64_t* full = keys ? &k_full[st] : &v_full[st];
+        int go = 1;
+        if (lane == 0) {
+          if (!mbar_wait_bounded(smem_addr(keys ? &k_empty[st] : &v_empty[st]), par ^ 1, aborted)) {
+            abort_flag = 1;
+            go = 0;
+          } else {
+            mbar_expect_tx(smem_addr(full), (uint32_t)n * 4096u);
+          }
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go || *aborted) break;
+        if (row >= 0) tma_load_2d(smem_addr(tile_s + st * TILE + half * SUB + c * 2048), map, half * 64, row, smem_addr(full));
+      }
+    } else if (warp == kMmaWarp && lane == 0) {
       constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV);                  // A and B K-major
       constexpr uint32_t idesc_pv = idesc_bf16(BQ, HD) | (1u << 16);    // B (values) MN-major
       bool ok = mbar_wait_bounded(smem_addr(&q_full), 0, aborted);
-      auto issue_s = [&](int j) {
-        const int st = j & 1, kst = j % kStages;
-        const uint32_t par = (uint32_t)((j >> 1) & 1);
-        if (!mbar_wait_bounded(smem_addr(&k_full[kst]), (uint32_t)((j / kStages) & 1), aborted)) return false;
-        if (!mbar_wait_bounded(smem_addr(&s_empty[st]), par ^ 1, aborted)) return false;
-        tc_fence_after();
+      int done_p[2] = {0, 0};                                            // P tiles of each query tile consumed so far
+      // S of query tile x for key tile j (the key stage must be full)
+      auto issue_s = [&](int x, int j) {
+        const int kst = j % kStages;
 #pragma unroll
         for (int dh = 0; dh < 2; ++dh) {
-          const uint64_t ad = smem_desc_sw128(smem_addr(q_s + dh * SUB));
+          const uint64_t ad = smem_desc_sw128(smem_addr(q_s + x * TILE + dh * SUB));
           const uint64_t bd = smem_desc_sw128(smem_addr(k_s + kst * TILE + dh * SUB));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + (uint32_t)(st * BKV), ad + 2 * k, bd + 2 * k, idesc_s, (dh | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) umma_bf16(tmem_base + (uint32_t)(x * BKV), ad + 2 * k, bd + 2 * k, idesc_s, (dh | k) != 0 ? 1u : 0u);
         }
-        umma_commit(smem_addr(&k_empty[kst]));
-        umma_commit(smem_addr(&s_full[st]));
-        return true;
+        umma_commit(smem_addr(&s_full[x]));
       };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        if (j + 1 < ntiles) ok = issue_s(j + 1);
-        if (!ok) break;
-        const int st = j & 1, vst = j % kStages;
-        if (!mbar_wait_bounded(smem_addr(&p_full[st]), (uint32_t)((j >> 1) & 1), aborted)) { ok = false; break; }
-        if (!mbar_wait_bounded(smem_addr(&v_full[vst]), (uint32_t)((j / kStages) & 1), aborted)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t bd = smem_desc_mn_sw128(smem_addr(v_s + vst * TILE + kk * 2048), SUB);
-          umma_bf16_a_tmem(tmem_o, tmem_p + (uint32_t)(st * 64 + kk * 8), bd, idesc_pv, (j | kk) != 0 ? 1u : 0u);
+      auto in_range = [&](int x, int j) { return j >= jlo_x[x] && j < jhi_x[x]; };
+      // key tile 0 for the query tiles that start there
+      if (ok && (in_range(0, 0) || in_range(1, 0))) {
+        ok = mbar_wait_bounded(smem_addr(&k_full[0]), 0, aborted);
+        if (ok) {
+          tc_fence_after();
+          if (in_range(0, 0)) issue_s(0, 0);
+          if (in_range(1, 0)) issue_s(1, 0);
+          umma_commit(smem_addr(&k_empty[0]));
         }
-        umma_commit(smem_addr(&v_empty[vst]));
-        umma_commit(smem_addr(&pv_done[st]));
+      }
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int vst = j % kStages, knext = (j + 1) % kStages;
+        const bool next_any = j + 1 < ntiles && (in_range(0, j + 1) || in_range(1, j + 1));
+        bool v_ready = false, k_ready = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (in_range(x, j)) {
+            if (!mbar_wait_bounded(smem_addr(&p_full[x]), (uint32_t)(done_p[x] & 1), aborted)) { ok = false; break; }
+            if (!v_ready) {
+              if (!mbar_wait_bounded(smem_addr(&v_full[vst]), (uint32_t)((j / kStages) & 1), aborted)) { ok = false; break; }
+              v_ready = true;
+            }
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint64_t bd = smem_desc_mn_sw128(smem_addr(v_s + vst * TILE + kk * 2048), SUB);
+              umma_bf16_a_tmem(tmem_base + (uint32_t)(256 + x * HD), tmem_base + (uint32_t)(x * BKV + kk * 8), bd, idesc_pv,
+                               (done_p[x] | kk) != 0 ? 1u : 0u);
+            }
+            ++done_p[x];
+            if (j + 1 == jhi_x[x]) umma_commit(smem_addr(&o_full[x]));
+          }
+          // S of the next key tile goes over this P: the tensor core runs them in the order issued
+          if (in_range(x, j + 1)) {
+            if (!k_ready) {
+              if (!mbar_wait_bounded(smem_addr(&k_full[knext]), (uint32_t)(((j + 1) / kStages) & 1), aborted)) { ok = false; break; }
+              k_ready = true;
+              tc_fence_after();
+            }
+            issue_s(x, j + 1);
+          }
+        }
+        if (!ok) break;
+        umma_commit(smem_addr(&v_empty[vst]));                  // tile j's values are read by what was issued so far
+        if (next_any || j + 1 < ntiles) umma_commit(smem_addr(&k_empty[knext]));
       }
       if (!ok) abort_flag = 1;
     }
   } else {
-    const int row = warp * 32 + lane;                         // query row of the tile = TMEM lane
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    const int p_row = min(p_first + row, p_last);
+    reg_more<kRegsSoftmax>();
+    const int x = warp >> 2;                                   // query tile of this warp group
+    const int row = (warp & 3) * 32 + lane;                    // query row of the tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + (uint32_t)(x * BKV), tmem_o = tmem_base + (uint32_t)(256 + x * HD);
+    const int p_first = x ? pf_x[1] : pf_x[0], pl = x ? pl_x[1] : pl_x[0];
+    const int jlo = x ? jlo_x[1] : jlo_x[0], jhi = x ? jhi_x[1] : jhi_x[0], rows_here = x ? rows_x[1] : rows_x[0];
+    const int p_row = min(p_first + row, pl);
     const int lo_row = window > 0 ? p_row - window + 1 : 0;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
-      const int buf = j & 1;
+    int n = 0;
+    for (int j = jlo; j < jhi; ++j, ++n) {
       const int k0 = kb + j * BKV;
-      const bool full_tile = k0 + BKV - 1 <= p_first && (window <= 0 || k0 >= p_last - window + 1);
-      bool ready = mbar_wait_bounded(smem_addr(&s_full[buf]), (uint32_t)((j >> 1) & 1), aborted);
+      const bool full_tile = k0 + BKV - 1 <= p_first && (window <= 0 || k0 >= pl - window + 1);
+      bool ready = mbar_wait_bounded(smem_addr(&s_full[x]), (uint32_t)(n & 1), aborted);
       if (__any_sync(0xffffffffu, !ready)) { ok = false; break; }
       tc_fence_after();
-      // The whole row of scores comes into registers at once (four loads in flight, one
-      // wait), which frees the S buffer for the tile after next right away.
+      // The whole row of scores comes into registers at once (four loads in flight, one wait).
       uint32_t sv[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_base + lane_addr + (uint32_t)(buf * BKV + c * 32), sv[c]);
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_addr + (uint32_t)(c * 32), sv[c]);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_addr(&s_empty[buf]));
       // the row maximum (raw scores; the scale is positive, so it is applied to the maximum
-      // alone).  Four running maxima keep the chain of dependent instructions short: a
-      // softmax warp has its scheduler to itself.
+      // alone).  Four running maxima keep the chain of dependent instructions short.
       float mx;
       {
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -297,15 +356,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       if (grow) m_used = m_new;
       const float m_eff = m_used == -INFINITY ? 0.f : m_used;
       l *= f;
-      // O may be touched, and P buffer j mod 2 overwritten, only after the products that
-      // still use them: P.V of tile j-2 read this P buffer; a rescale of O needs P.V of
-      // tile j-1 complete (which implies tile j-2).  Tile t signals pv_done[t mod 2]; its
-      // completions there are numbered t / 2, so a waiter is never two phases behind.
-      const bool rescale = j > 0 && __any_sync(0xffffffffu, f != 1.0f);
+      // O may be rescaled here without a wait: S of this key tile was issued after P.V of the tile
+      // before, and its completion (which s_full reports) covers everything issued before it.
+      const bool rescale = n > 0 && __any_sync(0xffffffffu, f != 1.0f);
       if (rescale) {
-        ready = mbar_wait_bounded(smem_addr(&pv_done[(j - 1) & 1]), (uint32_t)(((j - 1) >> 1) & 1), aborted);
-        if (__any_sync(0xffffffffu, !ready)) { ok = false; break; }
-        tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t v[32];
@@ -315,14 +369,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
           tmem_st32(tmem_o + lane_addr + (uint32_t)(c * 32), v);
         }
-        tmem_st_wait();
-      } else if (j > 1) {
-        ready = mbar_wait_bounded(smem_addr(&pv_done[j & 1]), (uint32_t)(((j - 2) >> 1) & 1), aborted);
-        if (__any_sync(0xffffffffu, !ready)) { ok = false; break; }
       }
       // exponentials (one fused multiply-add and one ex2 each; a masked score is -inf and
-      // gives 0), their sum in four partial sums, and P as bfloat16 in the swizzled
-      // K-major layout
+      // gives 0), their sum in four partial sums, and P as bfloat16 over the first half of S
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int h2 = 0; h2 < 2; ++h2) {
@@ -336,22 +385,22 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
             l4[(i >> 1) & 3] += e0 + e1;
             packed[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
           }
-        tmem_st32(tmem_p + lane_addr + (uint32_t)(buf * 64 + h2 * 32), packed);
+        tmem_st32(tmem_s + lane_addr + (uint32_t)(h2 * 32), packed);
       }
       tmem_st_wait();
       l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_addr(&p_full[buf]));
+      if (lane == 0) mbar_arrive(smem_addr(&p_full[x]));
     }
-    if (ok) {
-      const bool ready = mbar_wait_bounded(smem_addr(&pv_done[(ntiles - 1) & 1]), (uint32_t)(((ntiles - 1) >> 1) & 1), aborted);
+    if (ok && n > 0) {
+      const bool ready = mbar_wait_bounded(smem_addr(&o_full[x]), 0, aborted);
       if (__any_sync(0xffffffffu, !ready)) ok = false;
     }
-    if (ok) {
+    if (ok && n > 0) {
       tc_fence_after();
       const float inv = 1.0f / l;
-      __nv_bfloat16* orow = out + ((size_t)(t0 + mbeg + row) * nq + h) * HD;
+      __nv_bfloat16* orow = out + ((size_t)(t0 + mbeg + x * BQ + row) * nq + h) * HD;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
@@ -369,13 +418,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
             reinterpret_cast<uint4*>(orow + c * 32)[i] = make_uint4(p[4 * i], p[4 * i + 1], p[4 * i + 2], p[4 * i + 3]);
         }
       }
-    } else if (lane == 0) {
+    } else if (!ok && lane == 0) {
       abort_flag = 1;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -394,7 +443,7 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
                                              int skip_single, int* err, cudaStream_t s) {
   if (rows <= 0 || max_q_len <= 0) return 0;
   if (bt_width < 1) return ARLE_E_BADARG;
-  if (hd != HD || page_size % 16 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq > 65535 || rows > 65535)
+  if (hd != HD || page_size % 16 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || rows > 65535 || (max_q_len + BQ2 - 1) / BQ2 > 65535)
     return ARLE_E_UNSUPPORTED;
   if (q_row_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
     return ARLE_E_UNSUPPORTED;
@@ -406,14 +455,14 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
   if (rc) return rc;
   rc = tensor_map_2d_bf16(v_cache, cache_rows, HD, HD, 16, &mv);
   if (rc) return rc;
-  const size_t smem = (1 + 2 * kStages) * (size_t)TILE + 1024;
+  const size_t smem = (2 + 2 * kStages) * (size_t)TILE + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(paged_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((max_q_len + BQ - 1) / BQ, nq, rows);
+  dim3 grid(nq, (max_q_len + BQ2 - 1) / BQ2, rows);
   cudaError_t e = launch_kernel(paged_prefill_tc_kernel, grid, dim3(kThreads), smem, s, 1, mq, mk, mv, (__nv_bfloat16*)out,
                                 q_indptr, kv_lens, block_table, bt_stride, bt_width, nq, nkv, page_size,
                                 scale * 1.4426950408889634f, window, skip_single, err);
