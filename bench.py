@@ -236,6 +236,9 @@ def main() -> int:
     pf_tflops = flops / (pf_ms * 1e-3) / 1e12
     prefill = {"value": round(T * 1000.0 / pf_ms, 1), "tokens": T, "ms": round(pf_ms, 3),
                "frac": round(pf_tflops / pk["bf16_tflops"], 4), "tflops": round(pf_tflops, 1)}
+    # the step is timed in a loop of eight under the power cap: beside the burst figure, the sustained one
+    if pk.get("bf16_tflops_sustained"):
+        prefill["frac_of_sustained"] = round(pf_tflops / float(pk["bf16_tflops_sustained"]), 4)
 
     # end to end through the public entry point: host token ids in, host token ids out
     e2e = None
