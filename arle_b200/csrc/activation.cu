@@ -37,7 +37,10 @@ __global__ void silu_mul_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gu, _
     for (int k = 0; k < 4; ++k) {
       const __nv_bfloat162 p0 = k < 2 ? a2[2 * k] : b2[2 * k - 4], p1 = k < 2 ? a2[2 * k + 1] : b2[2 * k - 3];
       const float ga = __low2float(p0), gb = __low2float(p1);
-      o2[k] = __floats2bfloat162_rn(ga / (1.0f + expf(-ga)) * __high2float(p0), gb / (1.0f + expf(-gb)) * __high2float(p1));
+      // fast exponential and division (a few ulp of float32, far below the bfloat16 rounding that follows):
+      // with the exact ones the kernel was bound by arithmetic, not by memory
+      o2[k] = __floats2bfloat162_rn(__fdividef(ga, 1.0f + __expf(-ga)) * __high2float(p0),
+                                    __fdividef(gb, 1.0f + __expf(-gb)) * __high2float(p1));
     }
     *reinterpret_cast<uint4*>(out + t * (size_t)inter + 8 * c) = o4;
   }
