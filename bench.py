@@ -107,6 +107,8 @@ def main() -> int:
     ap.add_argument("--sizes", choices=sorted(SIZES), default="8b", help="layer sizes (default: Qwen3-8B, the contract's)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="profiling aid: run only the decode steps at --batch, or only the prefill")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: tokens each request holds")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: tokens of the prompt")
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--pdl", type=int, nargs="?", const=1, default=0,
                     help="programmatic dependent launch: 1 every kernel, 2 the weight-streaming products only")
@@ -121,6 +123,10 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.only == "all" and (args.context != CONTEXT or args.prefill_tokens != PREFILL_TOKENS):
+        print("bench.py: --context and --prefill-tokens go with --only decode / --only prefill; the full run keeps the contract's sizes")
+        return 2
+    globals()["CONTEXT"], globals()["PREFILL_TOKENS"] = args.context, args.prefill_tokens
 
     import torch
 
@@ -142,10 +148,10 @@ def main() -> int:
     spec = model.spec
     vocab = spec.vocab_size
     page = 16
-    max_batch = max(64, args.batch)
-    per_req = CONTEXT + args.steps + args.warmup + 64
+    max_batch = max(64, args.batch) if args.only == "all" else (args.batch if args.only == "decode" else 1)
+    per_req = max(CONTEXT + args.steps + args.warmup + 64, PREFILL_TOKENS + 64 if args.only != "decode" else 0)
     pages = max_batch * -(-per_req // page) + 64
-    runner = ModelRunner(model, page, pages, max_batch, CONTEXT * 2 + 1024, dev)
+    runner = ModelRunner(model, page, pages, max_batch, max(CONTEXT * 2 + 1024, per_req), dev)
     if not args.no_cuda_graph:
         runner.enable_graphs()
     for g in runner.cache.groups:
