@@ -203,6 +203,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       unsigned char* tile_s = keys ? k_s : v_s;
       // Page ids come 32 at a time, one per lane, with the next 32 already in flight, so that no
       // tile waits for a read of the block table; a lane picks its page with a shuffle.
+      int issued = 0;                                       // tiles whose loads were issued
       int p0 = kb / page_size;
       int cur = __ldg(bt + min(p0 + lane, bt_width - 1));
       int nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
@@ -237,6 +238,16 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
         go = __shfl_sync(0xffffffffu, go, 0);
         if (!go || *aborted) break;
         if (row >= 0) tma_load_2d(smem_addr(tile_s + st * TILE + half * SUB + c * 2048), map, half * 64, row, smem_addr(full));
+        ++issued;
+      }
+      // No copy may still be in flight when the CTA ends.  The issuing thread has waited for every tile
+      // unless a wait ran out, so this is free otherwise.
+      if (lane == 0) {
+        if (keys) mbar_wait_plain(smem_addr(&q_full), 0);
+        for (int s2 = 0; s2 < kStages && s2 < issued; ++s2) {
+          const int last = (issued - 1 - s2) / kStages * kStages + s2;       // last tile loaded into stage s2
+          mbar_wait_plain(smem_addr(keys ? &k_full[s2] : &v_full[s2]), (uint32_t)((last / kStages) & 1));
+        }
       }
     } else if (warp == kMmaWarp && lane == 0) {
       constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV);                  // A and B K-major
