@@ -43,7 +43,7 @@ constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = kConsumers + kProducerWarps * 32;
 constexpr int kXPad = 8;                     // elements of padding per x row (16 bytes): rows fall on different banks
 constexpr int kRowPad = 16;                  // bytes of padding per weight-row segment of a stage
-constexpr int kPartTiles = 16;                // tiles whose partial sums a CTA of a cluster keeps for one reduction at the end
+constexpr int kPartTiles = 16;                // tiles whose partial sums a CTA of a cluster keeps between two reductions
 constexpr uint32_t kSpinLimit = 1u << 22;    // polls of an mbarrier before giving up (a few hundred ms)
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -114,7 +114,6 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
   const int tiles = (r1 - r0 + 15) / 16;
   const int spt = (klen + KC - 1) / KC;                   // stages per 16-row tile
   const int total = tiles * spt;
-  const bool batched = csize > 1 && tiles <= kPartTiles;    // few tiles: one cluster reduction at the end
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -165,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       const int nvalid = min(16, r1 - rt);
       const int mine = max(0, min(kRowsPerProducer, nvalid - pw * kRowsPerProducer));     // rows of this warp
       if (lane == 0) {
-        if (!mbar_wait_bounded(smem_u32(&empty[slot]), par ^ 1)) timed_out = true;
+        if (!timed_out && !mbar_wait_bounded(smem_u32(&empty[slot]), par ^ 1)) timed_out = true;   // gives up once, not at every stage
         mbar_expect_tx(smem_u32(&full[slot]), (uint32_t)(mine * len * 2));
       }
       __syncwarp();
@@ -173,19 +172,27 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
         bulk_copy_g2s(smem_u32(stages + (size_t)slot * stage_bytes + (size_t)row * pitch), W + (size_t)(rt + row) * ldw + k0,
                       (uint32_t)(len * 2), smem_u32(&full[slot]));
       if (++slot == S) slot = 0, par ^= 1;
+      // The cluster's barriers are for all its threads.  The consumers meet twice after every kPartTiles
+      // tiles (and after the last): the producers meet them there, after the copies of those tiles are
+      // issued, and go on with the next tiles afterwards.  (Meeting them only at the very end would leave
+      // the consumers waiting at the first barrier for producers that wait for free stages.)
+      if (csize > 1 && c == spt - 1 && ((tile + 1) % kPartTiles == 0 || tile + 1 == tiles)) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        cluster.sync();
+      }
     }
     if (early && total <= S) {                              // fewer stages than the ring holds: x not fetched in the loop
       pdl_wait();
       fetch_x();
     }
     timed_out = __any_sync(0xffffffffu, timed_out);
-    if (csize > 1) {
-      // the cluster's barriers are for all threads: as many as the consumers pass
+    if (csize > 1 && spt == 0) {                            // a rank without a K range still meets the others
       cg::cluster_group cluster = cg::this_cluster();
-      if (!batched)
-        for (int tile = 0; tile < tiles; ++tile) cluster.sync();
-      cluster.sync();
-      if (batched) cluster.sync();
+      for (int ch = 0; ch < (tiles + kPartTiles - 1) / kPartTiles; ++ch) {
+        cluster.sync();
+        cluster.sync();
+      }
     }
     if (timed_out && lane == 0 && err) atomicExch(err, 1);
     return;
@@ -213,7 +220,7 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       acc2[n][0] = acc2[n][1] = acc2[n][2] = acc2[n][3] = 0.f;
     }
     for (int c = 0; c < spt; ++c) {
-      if (!mbar_wait_bounded(smem_u32(&full[slot]), par)) timed_out = true;
+      if (!timed_out && !mbar_wait_bounded(smem_u32(&full[slot]), par)) timed_out = true;
       const int kloc = c * KC;                              // offset inside this CTA's K range
       const int len = min(KC, klen - kloc);
       const uint32_t st = smem_u32(stages + (size_t)slot * stage_bytes);
@@ -264,41 +271,27 @@ __global__ void __launch_bounds__(kThreads, 1) skinny_gemm_kernel(
       } else if (csize == 1) {
         if (m < M && rt + row < r1) store_out<OutT>(out + (size_t)m * ldo + rt + row, s);
       } else {
-        part[(batched ? tile : (tile & 1)) * 16 * NT * 8 + tid] = s;
+        part[(tile % kPartTiles) * 16 * NT * 8 + tid] = s;
       }
     }
-    if (csize > 1 && !batched) {
-      // too many tiles to keep: rank 0 adds the ranks' sums tile by tile
+    if (csize > 1 && ((tile + 1) % kPartTiles == 0 || tile + 1 == tiles)) {
+      // one reduction for the last kPartTiles tiles (or fewer): rank 0 adds the ranks' sums, in rank order
       cg::cluster_group cluster = cg::this_cluster();
       cluster.sync();
       if (rank == 0 && tid < 16 * NT * 8) {
         const int row = tid & 15, m = tid >> 4;
-        float s = 0.f;
-        for (int rk = 0; rk < csize; ++rk) {
-          const float* remote = cluster.map_shared_rank(part, rk);
-          s += remote[(tile & 1) * 16 * NT * 8 + tid];
+        for (int t = tile / kPartTiles * kPartTiles; t <= tile; ++t) {
+          float s = 0.f;
+          for (int rk = 0; rk < csize; ++rk) {
+            const float* remote = cluster.map_shared_rank(part, rk);
+            s += remote[(t % kPartTiles) * 16 * NT * 8 + tid];
+          }
+          const int rt2 = r0 + t * 16;
+          if (m < M && rt2 + row < r1) store_out<OutT>(out + (size_t)m * ldo + rt2 + row, s);
         }
-        if (m < M && rt + row < r1) store_out<OutT>(out + (size_t)m * ldo + rt + row, s);
       }
+      cluster.sync();                                       // no CTA overwrites or leaves while its sums may still be read
     }
-  }
-  if (csize > 1) {
-    cg::cluster_group cluster = cg::this_cluster();
-    cluster.sync();
-    if (batched && rank == 0 && tid < 16 * NT * 8) {
-      // one reduction for all tiles: rank 0 adds the ranks' sums, in rank order
-      const int row = tid & 15, m = tid >> 4;
-      for (int tile = 0; tile < tiles; ++tile) {
-        float s = 0.f;
-        for (int rk = 0; rk < csize; ++rk) {
-          const float* remote = cluster.map_shared_rank(part, rk);
-          s += remote[tile * 16 * NT * 8 + tid];
-        }
-        const int rt = r0 + tile * 16;
-        if (m < M && rt + row < r1) store_out<OutT>(out + (size_t)m * ldo + rt + row, s);
-      }
-    }
-    if (batched) cluster.sync();                            // no CTA leaves while its partial sums may still be read
   }
   if (timed_out && err) atomicExch(err, 1);
 }

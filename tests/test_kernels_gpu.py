@@ -131,7 +131,9 @@ def test_gemm_bf16(M, N, K):
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 16, 32), (1, 4096, 4096), (8, 6144, 4096), (3, 1000, 192), (5, 37, 320),
-                                   (8, 301, 256), (7, 500, 12288), (8, 200, 12288), (8, 4100, 12288), (2, 151936, 128)])
+                                   (8, 301, 256), (7, 500, 12288), (8, 200, 12288), (8, 4100, 12288), (2, 151936, 128),
+                                   # K split over a cluster and more than sixteen tiles per cluster: several reductions
+                                   (4, 20000, 8192), (8, 12000, 16384)])
 def test_gemm_skinny_weight_streaming(M, N, K, out_dtype):
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
     assert ops.skinny_gemm_supported(x, w, torch.empty(M, N, dtype=out_dtype, device=DEV))
