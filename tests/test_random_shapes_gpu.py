@@ -1,9 +1,12 @@
-"""Differential tests of the fast attention kernels over random shapes: the streaming decode
+"""Tests over random shapes.  Differential tests of the fast attention kernels: the streaming decode
 kernel against the split-KV kernel, and the tcgen05 prefill kernel against the mma.sync one.
 Each pair shares no code beyond the cache layout, and each is compared with the plain reference
 at fixed shapes elsewhere; here the shapes are drawn at random (numbers of rows, heads and groups,
 page sizes, windows, lengths around the tile edges, prompt portions beside decoded rows, grid
-sizes), which is where the ways of sharing the work out among CTAs meet their corner cases."""
+sizes), which is where the ways of sharing the work out among CTAs meet their corner cases.
+And the weight-streaming product against float64 over random row counts, widths and depths
+(depths beside the edges of its stages, widths beside the number of SMs, depths long enough for
+a cluster together with many output rows)."""
 import math
 import random
 
@@ -84,3 +87,35 @@ def test_tcgen05_prefill_equals_mma_sync_prefill_on_random_shapes(seed):
         what = dict(nq=nq, nkv=nkv, ps=ps, q_lens=q_lens, lens=lens, window=window)
         assert torch.isfinite(a.float()).all(), what
         torch.testing.assert_close(a.float(), b.float(), rtol=3e-2, atol=2e-2, msg=lambda m: f"{m}\n{what}")
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_weight_streaming_gemm_on_random_shapes(seed):
+    rng = random.Random(seed)
+    for it in range(40):
+        M = rng.randint(1, 8)
+        K = 32 * rng.choice([1, 2, 3, 7, 16, 31, 32, 33, 64, 100, 128, 129, 160, 200, 256, 300, 384, 512])
+        N = rng.choice([1, 2, 15, 16, 17, 33, 100, 147, 148, 149, 296, 1000, 2368, 2369, 4096, 5000, 20000])
+        out_dtype = rng.choice([torch.bfloat16, torch.float32])
+        gated = rng.random() < 0.3
+        g = torch.Generator().manual_seed(100 * seed + it)
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+        what = dict(M=M, N=N, K=K, gated=gated, out=str(out_dtype))
+        if gated:
+            inter = max(1, N // 2)
+            w = (torch.randn(2 * inter, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+            gate_up = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device=DEV)
+            out = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device=DEV)
+            ops.gemm_silu_mul(x, w, gate_up, out)
+            gate, up = x.double() @ w[0::2].double().t(), x.double() @ w[1::2].double().t()
+            exp = gate / (1 + torch.exp(-gate)) * up
+            bound = 1.5e-2
+        else:
+            w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+            ops.gemm(x, w, out)
+            exp = x.double() @ w.double().t()
+            bound = 2e-5 if out_dtype == torch.float32 else 6e-3
+        ops.check_errors(DEV)                                  # no bounded wait ran out
+        err = (out.double() - exp).abs().max().item()
+        assert err <= bound * max(exp.abs().max().item(), 1.0), (what, err)
