@@ -7,9 +7,11 @@ window group gives pages back while the request lives and a full group does not.
 cklxx/arle has one group: one table per slot shared by all KV layers
 (crates/cuda-kernels/src/paged_kv.rs:63-70; infer/src/scheduler/cuda/core/construction.rs:194-202).
 
-Page layout inside a group: ``kv[layer, 0 or 1, page, kv_head, slot_in_page,
-head_dim]`` (keys at 0, values at 1), the reference's head-major page
-(paged_kv.rs:330-355).
+Page layout inside a group: one array per stream of the group's need (keys and
+values for attention), each ``[layer, page, head, slot_in_page, width]``, the
+reference's head-major page (paged_kv.rs:330-355).  A mixer with another per-token
+record (one compressed vector, keys and values of different widths) names its
+streams in its ``CacheNeed`` and gets arrays of those shapes under the same tables.
 
 A request holds one *slot* for its life.  The slot indexes the host-side block
 tables and the per-request state arrays that mixers may ask for (``StateNeed``);
@@ -41,12 +43,19 @@ class NoFreeSlot(RuntimeError):
 class LayerCacheView:
     """What a mixer sees of its cache layer during one step."""
 
-    k: torch.Tensor                 # [pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    streams: List[torch.Tensor]     # one [pages, heads, page_size, width] per stream of the mixer's CacheNeed
     page_size: int
     block_table: torch.Tensor       # int32 [rows of the step, max pages]; -1 where a window has passed
     slot_mapping: torch.Tensor      # int32 [tokens of the step]: page * page_size + slot_in_page
     writable: bool = True
+
+    @property
+    def k(self) -> torch.Tensor:    # attention's names for its two streams
+        return self.streams[0]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.streams[1]
 
 
 class CacheGroup:
@@ -56,8 +65,8 @@ class CacheGroup:
         self.layers = layers                      # cache-layer ids served by this group
         self.page_size = page_size
         self.pool = PagePool(num_pages)
-        self.kv = torch.zeros((len(layers), 2, num_pages, need.num_kv_heads, page_size, need.head_dim),
-                              dtype=dtype, device=device)
+        self.arrays = [torch.zeros((len(layers), num_pages, heads, page_size, width), dtype=dtype, device=device)
+                       for heads, width in need.arrays()]
         # host block tables, one row per slot; logical page -> physical page, -1 = not held
         self.table = np.full((max_slots, max_pages_per_request), -1, dtype=np.int32)
         self.first_held = np.zeros(max_slots, dtype=np.int64)     # first logical page still held
@@ -67,7 +76,7 @@ class CacheGroup:
         return max(0, -(-new_tokens // self.page_size) - int(self.num_logical[slot]))
 
     def bytes_per_page(self) -> int:
-        return len(self.layers) * 2 * self.need.num_kv_heads * self.page_size * self.need.head_dim * self.kv.element_size()
+        return len(self.layers) * self.need.elements_per_token() * self.page_size * self.arrays[0].element_size()
 
 
 class CacheManager:
@@ -80,6 +89,7 @@ class CacheManager:
         self.max_tokens_per_request = max_tokens_per_request
         self.device = torch.device(device)
         max_pages = -(-max_tokens_per_request // page_size)
+        self.max_pages_per_request = max_pages          # columns of every host block table
         by_key: Dict[tuple, List[int]] = {}
         for layer, need in enumerate(cache_needs):
             by_key.setdefault(need.group_key(), []).append(layer)
@@ -243,7 +253,7 @@ class CacheManager:
                    writable: bool) -> LayerCacheView:
         gi, j = self.layer_to_group[cache_layer]
         g = self.groups[gi]
-        return LayerCacheView(g.kv[j, 0], g.kv[j, 1], g.page_size, block_table, slot_mapping, writable)
+        return LayerCacheView([a[j] for a in g.arrays], g.page_size, block_table, slot_mapping, writable)
 
     def group_of_layer(self, cache_layer: int) -> int:
         return self.layer_to_group[cache_layer][0]

@@ -50,6 +50,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--mem-fraction-static", type=float, default=0.85)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--num-pages", type=int, default=None)
+    ap.add_argument("--kernel-set", default="fast", choices=["fast", "plain"],
+                    help="plain: run the general kernels only (to bisect a discrepancy)")
     sub = ap.add_subparsers(dest="command")
     run = sub.add_parser("run", help="run prompts and exit")
     g = run.add_mutually_exclusive_group(required=True)
@@ -90,7 +92,7 @@ def main(argv=None) -> int:
         max_num_batched_tokens=args.max_num_batched_tokens, chunked_prefill_size=args.chunked_prefill_size,
         max_prefill_tokens=args.max_prefill_tokens, prefill_max_requests=args.prefill_max_requests,
         scheduler_mixed_policy=args.scheduler_mixed_policy, max_tokens=args.max_tokens, seed=args.seed,
-        cuda_graph=not args.no_cuda_graph))
+        cuda_graph=not args.no_cuda_graph, kernel_set=args.kernel_set))
     sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
                         ignore_eos=args.ignore_eos, max_new_tokens=args.max_tokens)
     outs = eng.generate(prompts, sp)

@@ -36,6 +36,7 @@ class ModelSpec:
     stop_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
     ignored_tensors: Tuple[str, ...] = ()     # names a checkpoint may carry that the model does not read
+    kind: str = "decoder"                     # the registered model class that is built from this spec
 
     def validate(self) -> None:
         if not self.blocks or not self.schedule:

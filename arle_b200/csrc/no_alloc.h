@@ -27,7 +27,9 @@
  * device image.  Every GPU that loads the library holds those 4 MiB until the
  * process exits, used or not.  A call with rows * vocab beyond that maximum is
  * refused with ARLE_E_TOO_LARGE and launches nothing (4 rows of a 262,144-entry
- * vocabulary fit, or 6 rows of Qwen3's 151,936).
+ * vocabulary fit, or 6 rows of Qwen3's 151,936).  The limit applies only when
+ * temperatures are given: with temperature == NULL every row is an argmax, the
+ * array is not used, and any number of rows is taken.
  *
  * Rules for callers:
  *  - The function calls no cudaMalloc, cudaFree or other allocating routine, and

@@ -333,7 +333,8 @@ ARLE_API int arle_sample_static(const float* logits, int ld, int rows, int vocab
   if (rows <= 0) return 0;
   if (!logits || !out || vocab <= 0 || ld < vocab) return ARLE_E_BADARG;
   if (temperature && !uniform) return ARLE_E_BADARG;
-  if ((long long)rows * (long long)vocab > (long long)ARLE_SAMPLE_STATIC_MAX_FLOATS) return ARLE_E_TOO_LARGE;
+  // with no temperatures every row is greedy and the array is not touched: any size goes
+  if (temperature && (long long)rows * (long long)vocab > (long long)ARLE_SAMPLE_STATIC_MAX_FLOATS) return ARLE_E_TOO_LARGE;
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != 0) return rc;

@@ -32,6 +32,7 @@ class Workspace:
         self.device = torch.device(device)
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self.frozen = False
+        self.generation = 0            # counts (re)allocations: addresses handed out earlier may be stale after one
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -44,6 +45,7 @@ class Workspace:
                 raise RuntimeError(f"workspace buffer '{name}' would have to grow inside a captured graph")
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[:n].view(shape)
 
     def get_zeroed(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
@@ -59,6 +61,7 @@ class Workspace:
                 raise RuntimeError(f"workspace buffer '{name}' would have to grow inside a captured graph")
             buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
+            self.generation += 1
         return buf[:n].view(shape)
 
     def nbytes(self) -> int:

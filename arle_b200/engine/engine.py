@@ -38,6 +38,7 @@ class EngineOptions:
     max_tokens: int = 256                      # default max_new_tokens of a request
     seed: int = 42
     cuda_graph: bool = True
+    kernel_set: str = "fast"                   # "plain": the general kernels only, whatever the shapes
 
 
 @dataclass
@@ -63,8 +64,9 @@ class Engine:
         self.model = model
         max_seq = o.max_seq_len or model.spec.max_position
         per_page = self._bytes_per_page(model, o.page_size, dtype)
-        pages = o.num_pages if o.num_pages is not None else self._pages_from_memory(per_page, o, max_seq)
-        self.runner = ModelRunner(model, o.page_size, pages, o.num_slots, max_seq, o.device)
+        pages = o.num_pages if o.num_pages is not None else self._pages_from_memory(
+            per_page, o, max_seq, self._bytes_beside_the_cache(model, o))
+        self.runner = ModelRunner(model, o.page_size, pages, o.num_slots, max_seq, o.device, kernel_set=o.kernel_set)
         if o.cuda_graph and torch.device(o.device).type == "cuda":
             self.runner.enable_graphs()
         self.scheduler = Scheduler(self.runner.cache, SchedulerConfig(
@@ -78,17 +80,35 @@ class Engine:
     @staticmethod
     def _bytes_per_page(model, page_size: int, dtype) -> int:
         width = 2 if dtype == torch.bfloat16 else 4
-        return sum(2 * n.num_kv_heads * n.head_dim * page_size * width for n in model.cache_needs)
+        return sum(n.elements_per_token() * page_size * width for n in model.cache_needs)
 
     @staticmethod
-    def _pages_from_memory(per_page: int, o: EngineOptions, max_seq: int) -> int:
+    def _bytes_beside_the_cache(model, o: EngineOptions) -> int:
+        """What the engine will hold besides weights and pages: the per-request state arrays of
+        mixers that ask for them (one row per slot), the step buffers of the largest step the
+        scheduler may plan, and those of the widest captured decode step."""
+        state = 0
+        for n in model.state_needs:
+            elems = 1
+            for s_ in n.shape:
+                elems *= int(s_)
+            state += o.num_slots * elems * torch.empty((), dtype=n.dtype).element_size()
+        scratch = getattr(model, "scratch_bytes", None)
+        if scratch is None:
+            return state
+        steps = scratch(o.max_num_batched_tokens, min(o.num_slots, o.max_num_batched_tokens))
+        graphs = scratch(min(o.num_slots, 256), min(o.num_slots, 256)) if o.cuda_graph else 0
+        return state + steps + graphs
+
+    @staticmethod
+    def _pages_from_memory(per_page: int, o: EngineOptions, max_seq: int, beside: int = 0) -> int:
         if per_page == 0:
             return 1
         cap = o.num_slots * -(-max_seq // o.page_size)
         if torch.device(o.device).type != "cuda":
             return min(cap, 4096)
         free, total = torch.cuda.mem_get_info(torch.device(o.device))
-        budget = free - int((1.0 - o.mem_fraction_static) * total)
+        budget = free - int((1.0 - o.mem_fraction_static) * total) - beside
         if budget < per_page * o.num_slots:
             raise RuntimeError(f"not enough free device memory for the cache: {free >> 20} MiB free, "
                                f"mem_fraction_static={o.mem_fraction_static}")

@@ -5,6 +5,7 @@ import torch
 
 from ..config import config_from_dict, load_config
 from ..parts.model import DecoderModel
+from ..parts.registry import build_model
 from ..weights import load_weights, random_tensors
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -26,7 +27,7 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda") -> DecoderModel:
     dtype = parse_dtype(dtype)
     config = load_config(model_dir)
     spec = config.to_model_spec()
-    model = DecoderModel(spec)
+    model = build_model(spec)
     tensors = load_weights(model_dir, model.weight_decls(), spec.ignored_tensors)
     model.load(tensors, dtype, device)
     model.config = config
@@ -45,7 +46,7 @@ def random_model(config: dict, seed: int, dtype="bfloat16", device="cuda", sigma
             config["layer_types"] = config["layer_types"][:num_layers]
     cfg = config_from_dict(config)
     spec = cfg.to_model_spec()
-    model = DecoderModel(spec)
+    model = build_model(spec)
     tensors = random_tensors(model.weight_decls(), seed, sigma, gain_jitter, torch.bfloat16, device)
     model.load(tensors, dtype, device)
     model.config = cfg

@@ -31,6 +31,8 @@ def main(argv=None) -> int:
                     help="most tokens live requests hold at any time (each request rounded up to 64); sizes the cache")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (must divide 64)")
     ap.add_argument("--max-live", type=int, default=8, help="most requests live at a time")
+    ap.add_argument("--kernels", default="fast", choices=["fast", "plain"],
+                    help="fast: the kernels serving uses (shapes decide); plain: the general kernels only")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     if args.max_tokens <= 0 or args.page_size <= 0 or 64 % args.page_size:
@@ -51,7 +53,7 @@ def main(argv=None) -> int:
     os.makedirs(args.out, exist_ok=True)
     model = load_model(args.model, args.dtype, args.device)
     pages = -(-args.max_tokens // args.page_size)
-    runner = ModelRunner(model, args.page_size, pages, args.max_live, device=args.device)
+    runner = ModelRunner(model, args.page_size, pages, args.max_live, device=args.device, kernel_set=args.kernels)
     print(f"[trace_run] model loaded ({args.dtype}); cache: {pages} pages of {args.page_size} tokens",
           file=sys.stderr, flush=True)
     for line in sys.stdin:

@@ -17,6 +17,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..cache import CacheManager, OutOfPages
 from ..parts.model import DecoderModel
 from .batch import StepContext, StepEntry, Workspace
@@ -24,8 +25,11 @@ from .batch import StepContext, StepEntry, Workspace
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, page_size: int, num_pages: int, max_slots: int,
-                 max_tokens_per_request: Optional[int] = None, device="cuda"):
+                 max_tokens_per_request: Optional[int] = None, device="cuda", kernel_set: str = "fast"):
+        if kernel_set not in ("fast", "plain"):
+            raise ValueError(f"kernel_set must be 'fast' or 'plain', got {kernel_set!r}")
         self.model = model
+        self.kernel_set = kernel_set
         self.device = torch.device(device)
         self.cache = CacheManager(model.cache_needs, model.state_needs, page_size, num_pages, max_slots,
                                   max_tokens_per_request or model.spec.max_position, model.dtype, self.device)
@@ -40,6 +44,7 @@ class ModelRunner:
         self.tokens_run = 0
         self.graph_steps = 0
         self._graphs = None            # None: graphs off; else {(rows, table width): _DecodeGraph}
+        self._graph_ws = None
         self._max_graph_rows = 0
 
     # ----------------------------------------------------------------- graphs
@@ -52,6 +57,7 @@ class ModelRunner:
         if self.device.type != "cuda":
             raise RuntimeError("CUDA graphs need a CUDA device")
         self._graphs = {}
+        self._graph_ws = Workspace(self.device)
         self._max_graph_rows = max_rows
 
     def disable_graphs(self) -> None:
@@ -63,7 +69,8 @@ class ModelRunner:
         if any(len(e.tokens) != 1 or tuple(e.want) != (0,) for e in entries):
             return None
         pages = max(-(-(s + 1) // self.cache.page_size) for s in starts)
-        width = 1 << max(3, (pages - 1).bit_length())
+        # a power of two, but never wider than the host tables are
+        width = min(1 << max(3, (pages - 1).bit_length()), self.cache.max_pages_per_request)
         return (len(entries), width)
 
     def _run_graph(self, key, entries, starts):
@@ -105,7 +112,8 @@ class ModelRunner:
                 self.graph_steps += 1
             else:
                 ctx = self.ctx.build(entries, starts)
-                logits = self.model.forward(ctx)
+                with ops.use_kernel_set(self.kernel_set):
+                    logits = self.model.forward(ctx)
         except Exception:
             for e, s in zip(entries, starts):
                 self.cache.truncate(e.request, s)
@@ -120,16 +128,19 @@ class ModelRunner:
 
 class _DecodeGraph:
     """A captured decode step for one (row count, block-table width).  It owns its
-    step tables and its workspace, so their addresses never change; a replay
-    copies the step's tables into place and launches the graph."""
+    step tables, so their addresses never change; the scratch buffers are shared by
+    all graphs of a runner (they are as large as the widest captured step needs).
+    A replay copies the step's tables into place and launches the graph.  When a
+    shared buffer had to grow since the capture, the graph is captured again."""
 
     def __init__(self, runner: ModelRunner, table_width: int):
         self.runner = runner
         self.table_width = table_width
-        self.ws = Workspace(runner.device)
+        self.ws = runner._graph_ws
         self.ctx = StepContext(runner.cache, self.ws)
         self.ctx.last_token = runner.last_token
         self.graph = None
+        self.generation = -1
         self.logits = None
         self.launches = 0
 
@@ -137,17 +148,26 @@ class _DecodeGraph:
         from .. import ops
 
         ctx = self.ctx.build(entries, starts, self.table_width)
-        if self.graph is None:
+        if self.graph is None or self.generation != self.ws.generation:
+            # This step runs eagerly (which also brings every buffer to its size); the
+            # capture that follows records the same launches and executes nothing, so
+            # the step has run exactly once and its logits stand.
             model = self.runner.model
-            model.forward(ctx)                      # eager once: allocates every workspace buffer
-            torch.cuda.synchronize(self.runner.device)
-            self.ws.frozen = True
-            before = ops.launch_count()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self.logits = model.forward(ctx)
-            self.launches = ops.launch_count() - before
+            with ops.use_kernel_set(self.runner.kernel_set):
+                model.forward(ctx)
+                torch.cuda.synchronize(self.runner.device)
+                self.ws.frozen = True
+                try:
+                    before = ops.launch_count()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        self.logits = model.forward(ctx)
+                    self.launches = ops.launch_count() - before
+                finally:
+                    self.ws.frozen = False
             self.graph = graph
+            self.generation = self.ws.generation
+            return ctx, self.logits
         self.graph.replay()
         ops.add_launches(self.launches)
         return ctx, self.logits

@@ -52,6 +52,7 @@ _SIGNATURES = {
     "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                                         _I, _I, _I, _P, _P],
     "arle_gemm_f32": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "arle_gemm_plain_bf16": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_skinny": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_gemm_skinny_gated": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
@@ -120,6 +121,38 @@ def set_programmatic_launch(on) -> None:
     lib.arle_set_programmatic_launch.argtypes = [c_int]
     lib.arle_set_programmatic_launch.restype = None
     lib.arle_set_programmatic_launch(int(on))
+
+
+_KERNEL_SET = "fast"
+
+
+class use_kernel_set:
+    """``with use_kernel_set("plain"):`` makes every dispatch inside it take the general
+    kernels (plain FFMA products with float32 sums, the general paged attention, the gate
+    as a kernel of its own), whatever the shapes; "fast" (the default) lets the shapes
+    decide.  The plain set is the yardstick a bfloat16 discrepancy is bisected with:
+    the same trace on both sets differs only by the fast kernels.  cklxx/arle chooses a
+    backend per operation in the same place (infer/src/ops.rs:135-269)."""
+
+    def __init__(self, name: str):
+        if name not in ("fast", "plain"):
+            raise ValueError(f"kernel set must be 'fast' or 'plain', got {name!r}")
+        self.name = name
+
+    def __enter__(self):
+        global _KERNEL_SET
+        self._before = _KERNEL_SET
+        _KERNEL_SET = self.name
+        return self
+
+    def __exit__(self, *exc):
+        global _KERNEL_SET
+        _KERNEL_SET = self._before
+        return False
+
+
+def kernel_set() -> str:
+    return _KERNEL_SET
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -228,6 +261,12 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm: bfloat16 path needs bfloat16 operands, got {x.dtype} and {w.dtype}")
     _ptr(x), _ptr(w), _ptr(out)
+    if _KERNEL_SET == "plain":
+        if x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("gemm: operands need unit inner strides")
+        _check(library().arle_gemm_plain_bf16(_ptr(x), _ptr(w), _ptr(out), _dt(out), M, N, K, x.stride(0), w.stride(0),
+                                              out.stride(0), _stream()), "gemm_plain_bf16")
+        return
     if skinny_gemm_supported(x, w, out):
         _check(library().arle_gemm_skinny(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out), out.stride(0),
                                           M, N, K, _ptr(error_flag(x.device)), _stream()), "gemm_skinny")
@@ -335,7 +374,7 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
     _i32(positions, "positions"), _i32(row_of_token, "row_of_token"), _i32(block_table, "block_table")
     if block_table.stride(1) != 1:
         raise KernelError("paged_attention: block table rows must be contiguous")
-    if batch is not None and fast_attention_supported(q, nq, nkv, hd):
+    if batch is not None and _KERNEL_SET == "fast" and fast_attention_supported(q, nq, nkv, hd):
         if batch.max_q_len > 1:
             prefill = paged_attention_prefill_tc if tc_attention_supported(q, hd, page_size) else paged_attention_prefill
             prefill(q, out, k_cache, v_cache, batch.q_indptr, batch.kv_lens, block_table, nq, nkv, hd, page_size, scale,
@@ -349,7 +388,7 @@ def paged_attention(q, out, k_cache, v_cache, positions, row_of_token, block_tab
                 batch.ws.get("attn_piece_ml", (slots * 2,), torch.float32),
                 batch.ws.get_zeroed("attn_piece_counters", (batch.num_rows * nkv,), torch.int32), ctas)
         elif batch.num_single > 0:
-            splits = decode_splits(batch.num_rows, nkv, block_table.shape[1] * page_size)
+            splits = decode_splits(batch.num_rows, nkv, block_table.shape[1] * page_size, q.device)
             part_o = part_ml = counters = None
             if splits > 1:
                 part_o = batch.ws.get("attn_part_o", (batch.num_rows * nq * splits * hd,), torch.float32)
@@ -395,8 +434,8 @@ def paged_attention_prefill_tc(q, out, k_cache, v_cache, q_indptr, kv_lens, bloc
 _SM_COUNT: dict = {}
 
 
-def sm_count(device) -> int:
-    device = torch.device(device)
+def sm_count(device=None) -> int:
+    device = torch.device(device if device is not None else "cuda")
     key = device.index if device.index is not None else torch.cuda.current_device()
     if key not in _SM_COUNT:
         _SM_COUNT[key] = torch.cuda.get_device_properties(key).multi_processor_count
@@ -435,11 +474,11 @@ def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, b
         _stream()), "paged_attention_decode_stream")
 
 
-def decode_splits(rows: int, nkv: int, kv_bound: int) -> int:
+def decode_splits(rows: int, nkv: int, kv_bound: int, device=None) -> int:
     """Splits along the keys.  With enough work for four waves of CTAs (three CTAs
     per SM), one split per 512 keys; otherwise as many splits as fill one wave.
     Never more than one per 64-key tile of the longest request the tables allow."""
-    slots = 148 * 3
+    slots = sm_count(device) * 3
     base = max(1, rows * nkv)
     by_len = -(-kv_bound // 512)
     splits = by_len if base * by_len >= 4 * slots else max(1, slots // base)
@@ -486,8 +525,8 @@ def gemm_silu_mul(x: torch.Tensor, w: torch.Tensor, gate_up: torch.Tensor, out: 
     T, I = out.shape
     if w.shape[0] != 2 * I or gate_up.shape != (T, 2 * I):
         raise KernelError(f"gemm_silu_mul: shapes w {tuple(w.shape)} gate_up {tuple(gate_up.shape)} out {tuple(out.shape)}")
-    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and skinny_gemm_supported(x, w, out)
-            and gated_gemm_fits(x.shape[1])):
+    if (_KERNEL_SET == "fast" and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and skinny_gemm_supported(x, w, out) and gated_gemm_fits(x.shape[1])):
         _ptr(x), _ptr(w), _ptr(out)
         _check(library().arle_gemm_skinny_gated(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out), out.stride(0),
                                                 T, 2 * I, x.shape[1], _ptr(error_flag(x.device)), _stream()),

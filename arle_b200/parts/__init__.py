@@ -4,10 +4,10 @@ from .block import PreNormBlock, PreNormBlockSpec
 from .mlp import GatedMlp, GatedMlpSpec
 from .model import DecoderModel, ResidualStream, declared_weights
 from .norm import RmsNorm, RmsNormSpec
-from .registry import build_part, register_part, registered_parts
+from .registry import build_model, build_part, register_model, register_part, registered_models, registered_parts
 from .rotary import Rotary, RotarySpec
 
 __all__ = ["Attention", "AttentionSpec", "Block", "CacheNeed", "FeedForward", "Mixer", "Norm", "Part",
            "PositionEncoding", "StateNeed", "WeightDecl", "PreNormBlock", "PreNormBlockSpec", "GatedMlp",
            "GatedMlpSpec", "DecoderModel", "ResidualStream", "declared_weights", "RmsNorm", "RmsNormSpec",
-           "build_part", "register_part", "registered_parts", "Rotary", "RotarySpec"]
+           "build_model", "build_part", "register_model", "register_part", "registered_models", "registered_parts", "Rotary", "RotarySpec"]

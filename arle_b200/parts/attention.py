@@ -74,6 +74,10 @@ class Attention(Mixer):
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
 
+    def scratch_elements_per_token(self):
+        s = self.spec
+        return (2 * s.num_heads + 2 * s.num_kv_heads) * s.head_dim + s.hidden_size
+
     # ------------------------------------------------------------------ cache
     def cache_need(self):
         return CacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)

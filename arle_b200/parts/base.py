@@ -47,17 +47,33 @@ class WeightDecl:
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """Paged keys and values a mixer wants for each token it has seen.
+    """Paged per-token arrays a mixer wants for each token it has seen.
+
+    Attention keeps two, keys and values, each ``[num_kv_heads, head_dim]`` per token:
+    ``CacheNeed(num_kv_heads, head_dim)``.  A mixer whose per-token record has another
+    form names its arrays itself in ``streams``, one ``(heads, width)`` per array: one
+    compressed vector per token is ``streams=((1, width),)``; keys and values of
+    different widths are two different entries.  The cache manager gives every stream a
+    paged array ``[pages, heads, page_size, width]`` per layer, all under one block table.
 
     ``window`` None keeps every token; an integer keeps only what the last
     ``window`` positions can still see, so older pages go back to the pool."""
 
-    num_kv_heads: int
-    head_dim: int
+    num_kv_heads: int = 0
+    head_dim: int = 0
     window: Optional[int] = None
+    streams: Optional[Tuple[Tuple[int, int], ...]] = None
+
+    def arrays(self) -> Tuple[Tuple[int, int], ...]:
+        if self.streams is not None:
+            return tuple((int(h), int(w)) for h, w in self.streams)
+        return ((self.num_kv_heads, self.head_dim), (self.num_kv_heads, self.head_dim))
+
+    def elements_per_token(self) -> int:
+        return sum(h * w for h, w in self.arrays())
 
     def group_key(self):
-        return (self.num_kv_heads, self.head_dim, self.window)
+        return (self.arrays(), self.window)
 
 
 @dataclass(frozen=True)
@@ -82,6 +98,11 @@ class Part:
 
     def weight_bytes(self) -> int:
         """Bytes of weights one forward pass reads (for roofline accounting)."""
+        return 0
+
+    def scratch_elements_per_token(self) -> int:
+        """Activation elements per token this part keeps in step buffers (an estimate the
+        engine uses to leave memory for them beside the cache)."""
         return 0
 
 

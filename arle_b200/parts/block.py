@@ -40,6 +40,11 @@ class PreNormBlock(Block):
     def weight_bytes(self):
         return sum(p.weight_bytes() for p in self._parts)
 
+    def scratch_elements_per_token(self):
+        # the two normalised inputs and the larger of the two branches' buffers
+        return (self.mixer_norm.scratch_elements_per_token() + self.ffn_norm.scratch_elements_per_token()
+                + max(self.mixer.scratch_elements_per_token(), self.ffn.scratch_elements_per_token()))
+
     def forward(self, stream, ctx, cache, state):
         h = stream.normed(self.mixer_norm, "normed_a")
         stream.add(self.mixer.forward(h, ctx, cache, state))

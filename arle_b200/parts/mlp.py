@@ -48,6 +48,9 @@ class GatedMlp(FeedForward):
     def weight_bytes(self):
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
+    def scratch_elements_per_token(self):
+        return 3 * self.spec.intermediate_size + self.spec.hidden_size
+
     def forward(self, x, ctx):
         s = self.spec
         T = x.shape[0]

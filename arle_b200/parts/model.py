@@ -15,7 +15,7 @@ import torch
 from .. import ops
 from ..config.model_spec import ModelSpec
 from .base import WeightDecl
-from .registry import build_part
+from .registry import build_part, register_model
 
 
 class ResidualStream:
@@ -83,8 +83,8 @@ class DecoderModel:
             if e.keys_of is not None:
                 src = spec.schedule[e.keys_of]
                 src_need = self.blocks[src.block].mixer.cache_need()
-                if need is None or src_need is None or need.group_key()[:2] != src_need.group_key()[:2]:
-                    raise ValueError(f"schedule entry {i} cannot read the cache of entry {e.keys_of}: head layouts differ")
+                if need is None or src_need is None or need.arrays() != src_need.arrays():
+                    raise ValueError(f"schedule entry {i} cannot read the cache of entry {e.keys_of}: their per-token arrays differ")
                 self.entry_cache_layer.append(self.entry_cache_layer[e.keys_of])
             elif need is not None:
                 self.entry_cache_layer.append(len(self.cache_needs))
@@ -127,20 +127,42 @@ class DecoderModel:
         return n
 
     # ---------------------------------------------------------------- forward
-    def forward(self, ctx) -> Optional[torch.Tensor]:
-        T, H = ctx.num_tokens, self.spec.hidden_size
-        resid = ctx.ws.get("residual", (T, H), torch.float32)
+    # The forward pass in three steps that a model class of another arrangement may replace
+    # one by one: the residual the blocks start from, the scheduled blocks, the logits.
+    def embed_tokens(self, ctx) -> torch.Tensor:
+        """The float32 residual [T, hidden] of this step's tokens."""
+        resid = ctx.ws.get("residual", (ctx.num_tokens, self.spec.hidden_size), torch.float32)
         ops.embedding(ctx.token_ids, self.embed, resid, None, getattr(ctx, "last_token", None),
                       getattr(ctx, "slot_of_token", None))
-        stream = ResidualStream(resid, ctx.ws, self.dtype)
+        return resid
+
+    def run_blocks(self, stream: ResidualStream, ctx) -> None:
         for i, e in enumerate(self.spec.schedule):
             cl = self.entry_cache_layer[i]
             cache = ctx.cache_view(cl, writable=e.keys_of is None) if cl is not None else None
             st = ctx.state_view(self.entry_state[i]) if self.entry_state[i] is not None else None
             self.blocks[e.block].forward(stream, ctx, cache, st)
-        if ctx.num_wanted == 0:
-            return None
+
+    def logits_at_wanted(self, stream: ResidualStream, ctx) -> torch.Tensor:
         final = stream.normed_rows(self.final_norm, ctx.want_rows, "final_normed")
         logits = ctx.ws.get("logits", (ctx.num_wanted, self.spec.vocab_size), torch.float32)
         ops.gemm(final, self.head, logits)
         return logits
+
+    def forward(self, ctx) -> Optional[torch.Tensor]:
+        stream = ResidualStream(self.embed_tokens(ctx), ctx.ws, self.dtype)
+        self.run_blocks(stream, ctx)
+        if ctx.num_wanted == 0:
+            return None
+        return self.logits_at_wanted(stream, ctx)
+
+    def scratch_bytes(self, tokens: int, wanted: int) -> int:
+        """Bytes of step buffers a step of this many tokens and wanted rows holds (an upper
+        estimate from the widest block), so that the engine can leave room for them."""
+        act = 2 if self.dtype == torch.bfloat16 else 4
+        widest = max((b.scratch_elements_per_token() for b in self.blocks), default=0)
+        H = self.spec.hidden_size
+        return tokens * (4 * H + widest * act) + wanted * (self.spec.vocab_size * 4 + H * act)
+
+
+register_model("decoder", DecoderModel)

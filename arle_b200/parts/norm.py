@@ -35,6 +35,9 @@ class RmsNorm(Norm):
     def weight_bytes(self):
         return self.weight.numel() * 4
 
+    def scratch_elements_per_token(self):
+        return self.spec.size
+
     def apply(self, resid, delta, rows, out, write_resid: bool):
         """out = norm(resid (+ delta)) on all rows or on ``rows``; see ops.rmsnorm."""
         ops.rmsnorm(resid, delta, rows, self.weight, self.eps, out, write_resid)

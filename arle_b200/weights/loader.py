@@ -66,8 +66,11 @@ def load_weights(model_dir: str, decls: Sequence[WeightDecl], ignored: Iterable[
                  device="cpu") -> Dict[str, torch.Tensor]:
     files, weight_map = _open_files(model_dir)
     where = {}
+    twice = []
     for fn, f in files.items():
         for n in f.names():
+            if n in where:
+                twice.append(f"tensor {n} is stored in two files: {os.path.basename(where[n].path)} and {os.path.basename(f.path)}")
             where[n] = f
     wanted = {d.name: d for d in decls}
     ignored = set(ignored)
@@ -79,8 +82,8 @@ def load_weights(model_dir: str, decls: Sequence[WeightDecl], ignored: Iterable[
             _, shape = where[n].info(n)
             if tuple(shape) != tuple(d.shape):
                 wrong.append((n, d.shape, shape))
-    if missing or unexpected or wrong:
-        raise WeightError(model_dir, missing, unexpected, wrong)
+    if missing or unexpected or wrong or twice:
+        raise WeightError(model_dir, missing, unexpected, wrong, twice)
     out = {}
     for n, d in wanted.items():
         t = where[n].tensor(n)

@@ -155,7 +155,8 @@ def main() -> int:
     if not args.no_cuda_graph:
         runner.enable_graphs()
     for g in runner.cache.groups:
-        g.kv.normal_(0.0, 0.5)                                   # synthetic cache contents
+        for a in g.arrays:
+            a.normal_(0.0, 0.5)                                  # synthetic cache contents
     sampler = Sampler(vocab, dev)
     gen = torch.Generator().manual_seed(1)
     weight_bytes = model.weight_bytes_per_step()

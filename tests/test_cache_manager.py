@@ -155,3 +155,24 @@ def test_random_orders_keep_every_page_accounted(seed):
         m.free_request(rid)
     m.check()
     assert all(f == 24 for f in m.free_pages())
+
+
+def test_a_need_names_its_own_per_token_arrays():
+    """Attention keeps keys and values of one shape; a mixer may name other arrays (one compressed
+    vector per token; keys wider than values).  Each stream gets pages of its own shape per layer,
+    all under the group's one block table, and the bytes per token follow."""
+    needs = [CacheNeed(2, 8), CacheNeed(streams=((1, 24),)), CacheNeed(streams=((2, 16), (2, 8))), CacheNeed(streams=((1, 24),))]
+    cm = CacheManager(needs, [], 4, 10, 2, 40, torch.float32, "cpu")
+    assert [len(g.arrays) for g in cm.groups] == [2, 1, 2] and [g.layers for g in cm.groups] == [[0], [1, 3], [2]]
+    assert [tuple(a.shape) for a in cm.groups[1].arrays] == [(2, 10, 1, 4, 24)]
+    assert [tuple(a.shape) for a in cm.groups[2].arrays] == [(1, 10, 2, 4, 16), (1, 10, 2, 4, 8)]
+    assert cm.bytes_per_token() == (2 * 2 * 8 + 2 * 24 + 2 * 16 + 2 * 8) * 4
+    cm.add_request("a")
+    cm.append([("a", 9)])
+    bt = torch.zeros(1, 3, dtype=torch.int32)
+    view = cm.layer_view(3, bt, torch.zeros(9, dtype=torch.int32), True)
+    assert len(view.streams) == 1 and tuple(view.streams[0].shape) == (10, 1, 4, 24)
+    view = cm.layer_view(2, bt, torch.zeros(9, dtype=torch.int32), True)
+    assert tuple(view.k.shape) == (10, 2, 4, 16) and tuple(view.v.shape) == (10, 2, 4, 8)
+    cm.free_request("a")
+    cm.check()

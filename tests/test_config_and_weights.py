@@ -178,6 +178,12 @@ def test_sharded_checkpoint(tmp_path):
         json.dump({"weight_map": wm}, fh)
     spec = load_config(d).to_model_spec()
     assert len(load_weights(d, declared_weights(spec))) == len(names)
+    # a tensor stored in two shards is an error, named with both files
+    write_safetensors(os.path.join(d, "model-1.safetensors"),
+                      {n: f.tensor(n).clone() for n in names[half:] + names[:1]})
+    with pytest.raises(WeightError) as e:
+        load_weights(d, declared_weights(spec))
+    assert names[0] in str(e.value) and "model-0.safetensors" in str(e.value) and "model-1.safetensors" in str(e.value)
 
 
 def test_random_model_is_seeded_and_order_free(tmp_path):
@@ -194,6 +200,28 @@ def test_random_model_is_seeded_and_order_free(tmp_path):
     g = fa.tensor("model.norm.weight").float()
     assert g.min() >= 0.8 - 1e-2 and g.max() <= 1.2 + 1e-2 and abs(fa.tensor("lm_head.weight").float().std() - 0.03) < 3e-3
     assert json.load(open(os.path.join(a, "config.json"))) == CONFIGS["B"]
+
+
+def test_random_values_do_not_depend_on_the_device():
+    """The generator is integer arithmetic on (seed, name, element index): chunks computed apart
+    equal the whole, and (on a machine with a GPU) the GPU's values equal the CPU's bit for bit."""
+    from arle_b200.weights import random_init as ri
+    from arle_b200.parts.base import WeightDecl
+
+    decls = [WeightDecl("w", (300, 70)), WeightDecl("g", (130,), init="gain")]
+    whole = random_tensors(decls, 9, 0.02, 0.1)
+    old = ri._CHUNK
+    ri._CHUNK = 1000
+    try:
+        pieces = random_tensors(decls, 9, 0.02, 0.1)
+    finally:
+        ri._CHUNK = old
+    assert all(torch.equal(whole[k], pieces[k]) for k in whole)
+    w = random_tensors(decls[:1], 9, 1.0, 0.1, dtype=torch.float32)["w"].double()
+    assert abs(w.mean()) < 0.02 and abs(w.std() - 1.0) < 0.02 and 2.7 < (w ** 4).mean() < 3.1 and w.abs().max() < 6.0
+    if torch.cuda.is_available():
+        gpu = random_tensors(decls, 9, 0.02, 0.1, device="cuda")
+        assert all(torch.equal(whole[k], gpu[k].cpu()) for k in whole)
 
 
 def test_command_line_writes_a_random_model_folder(tmp_path):

@@ -83,6 +83,49 @@ def test_cuttings_around_the_kernels_cpu(name, dtype, cut, tmp_path_factory, cpu
     check(name, dtype, cut, "cpu", tmp_path_factory)
 
 
+def check_preempted(name, dtype, device, tmp_path_factory):
+    d, reqs, oracle = model_and_oracle(name, tmp_path_factory)
+    steps = traces.preempted(reqs)
+    victim = max(reqs, key=lambda r: len(reqs[r]))
+    ps = PAGE_SIZES[name]
+    model = load_model(d, dtype, device)
+    runner = ModelRunner(model, ps, traces.peak_tokens(steps) // ps, 4, device=device)
+    rows = traces.run_trace_by_position(runner, steps)
+    runner.cache.check()
+    assert all(g.pool.num_free == g.pool.num_pages for g in runner.cache.groups), "pages not given back"
+    seen = {}
+    for r, pos, row in rows:
+        err = (row.double() - oracle[r][pos]).abs().max().item()
+        assert err <= ATOL[dtype], f"{name} {dtype}: request {r} position {pos} (time {seen.get((r, pos), 0) + 1}): error {err:.3g}"
+        seen[(r, pos)] = seen.get((r, pos), 0) + 1
+    assert all(seen.get((r, p), 0) >= 1 for r, t in reqs.items() for p in range(len(t)))
+    assert seen[(victim, 0)] == 2 and seen[(victim, len(reqs[victim]) - 1)] == 1      # computed again from its first token
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["B", "C", "D", "E", "F"])
+def test_an_ended_request_starts_again_gpu(name, dtype, tmp_path_factory):
+    """A request is ended half-way, others take its pages, and it is prefilled again from its first
+    token under the same name (preemption by recomputation as a trace)."""
+    check_preempted(name, dtype, "cuda", tmp_path_factory)
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_an_ended_request_starts_again_cpu(name, tmp_path_factory, cpu_kernels):
+    check_preempted(name, torch.float32, "cpu", tmp_path_factory)
+
+
+def test_preempted_trace_shape():
+    reqs = traces.make_requests(100, LENGTHS["B"], seed=5)
+    steps = traces.preempted(reqs)
+    victim = max(reqs, key=lambda r: len(reqs[r]))
+    ends = [s["step"] for s in steps if victim in s["end"]]
+    starts = [s["step"] for s in steps for e in s["entries"] if e["id"] == victim and e["tokens"][:2] == reqs[victim][:2]]
+    assert len(ends) == 2 and len(starts) == 2 and starts[1] > ends[0]
+    assert traces.peak_tokens(steps) < sum(-(-len(t) // 64) * 64 for t in reqs.values())
+
+
 def test_mixed_trace_reuses_pages():
     reqs = traces.make_requests(100, LENGTHS["A"], seed=5)
     steps = traces.mixed(reqs, seed=3)
@@ -90,3 +133,28 @@ def test_mixed_trace_reuses_pages():
     assert max(len(s["entries"]) for s in steps) >= 3
     assert any(len(e["tokens"]) == 1 for s in steps for e in s["entries"]) and \
         any(len(e["tokens"]) == 2 for s in steps for e in s["entries"])
+
+
+def test_graph_table_width_never_exceeds_the_host_table(tmp_path_factory, cpu_kernels):
+    """A captured decode step fixes its block-table width at a power of two; the host tables
+    have ceil(limit / page) columns, which need not be one.  The width must be cut to them."""
+    from arle_b200.engine import StepContext, StepEntry, Workspace
+
+    d, reqs, oracle = model_and_oracle("A", tmp_path_factory)
+    model = load_model(d, torch.float32, "cpu")
+    runner = ModelRunner(model, 4, 64, 2, max_tokens_per_request=40, device="cpu")       # 10 columns
+    runner._graphs, runner._max_graph_rows = {}, 8                                       # as enable_graphs() leaves them
+    toks = reqs["r4"][:34]
+    runner.step([StepEntry("x", toks[:33], ())])
+    entries = [StepEntry("x", toks[33:34], (0,))]
+    key = runner._graph_key(entries, [33])               # 9 pages: the next power of two is 16
+    assert key == (1, 10)
+    runner.cache.append([("x", 1)])
+    ctx = StepContext(runner.cache, Workspace("cpu")).build(entries, [33], key[1])
+    assert tuple(ctx.groups[0].block_table.shape) == (1, 10)
+    logits = model.forward(ctx)
+    assert (logits[0].double() - oracle["r4"][33]).abs().max().item() <= ATOL[torch.float32]
+    # fewer columns than the narrowest graph is wide
+    small = ModelRunner(model, 4, 64, 2, max_tokens_per_request=20, device="cpu")        # 5 columns
+    small._graphs, small._max_graph_rows = {}, 8
+    assert small._graph_key([StepEntry("y", [3], (0,))], [2]) == (1, 5)

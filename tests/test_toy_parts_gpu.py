@@ -17,8 +17,8 @@ import plain_qwen3 as plain
 from arle_b200.config import ModelSpec, ScheduleEntry
 from arle_b200.engine import ModelRunner, StepEntry
 from arle_b200.parts import (AttentionSpec, DecoderModel, GatedMlpSpec, PreNormBlockSpec, RmsNormSpec, WeightDecl,
-                             register_part)
-from arle_b200.parts.base import FeedForward, PositionEncoding
+                             build_model, register_model, register_part)
+from arle_b200.parts.base import CacheNeed, FeedForward, Mixer, PositionEncoding
 from arle_b200.weights import random_tensors
 
 pytestmark = pytest.mark.gpu
@@ -209,3 +209,148 @@ def test_toy_routed_feed_forward_and_position_encoding_in_one_model(dtype, route
         assert err.max().item() < tol, f"first wrong position {int((err >= tol).nonzero()[0])}: {err.max().item()}"
     runner.end_request("a")
     runner.end_request("b")
+
+
+# ------------------------------------------------------------------ a mixer with one compressed vector per token
+@dataclass(frozen=True)
+class LatentMixerSpec:
+    prefix: str
+    hidden_size: int
+    latent: int
+    kind: ClassVar[str] = "test_latent_mixer"
+
+
+class LatentMixer(Mixer):
+    """Keeps ONE vector of ``latent`` numbers per token in the paged cache (not keys and values of
+    equal shape): c_t = x_t Wc.  A query q_t = x_t Wq scores the vectors of its request up to its own
+    position, and the output is (softmax(q c^T / sqrt(latent)) c) Wo.  Written with torch operations
+    over the cache manager's pages, block table and slot mapping."""
+
+    def __init__(self, spec):
+        self.spec = spec
+
+    def weight_decls(self):
+        s, p = self.spec, self.spec.prefix
+        return (WeightDecl(p + "wc.weight", (s.latent, s.hidden_size)), WeightDecl(p + "wq.weight", (s.latent, s.hidden_size)),
+                WeightDecl(p + "wo.weight", (s.hidden_size, s.latent)))
+
+    def load(self, tensors, dtype, device):
+        p = self.spec.prefix
+        self.wc, self.wq, self.wo = (tensors[p + n + ".weight"].to(device=device, dtype=torch.float32) for n in ("wc", "wq", "wo"))
+
+    def cache_need(self):
+        return CacheNeed(streams=((1, self.spec.latent),))
+
+    def forward(self, x, ctx, cache, state):
+        L = self.spec.latent
+        assert len(cache.streams) == 1 and tuple(cache.streams[0].shape[1:]) == (1, cache.page_size, L)
+        pages = cache.streams[0]
+        flat = pages.view(-1, L)                                     # one head: token slot = page * page_size + offset
+        xf = x.float()
+        flat[cache.slot_mapping.long()] = (xf @ self.wc.t()).to(pages.dtype)
+        q = xf @ self.wq.t()
+        out = torch.zeros(x.shape[0], L, device=x.device)
+        at = 0
+        for r, (n, kv) in enumerate(zip(ctx.q_lens, ctx.kv_lens_host)):
+            held = cache.block_table[r, : -(-kv // cache.page_size)].long()
+            c = pages[held, 0].reshape(-1, L)[:kv].float()
+            sc = q[at:at + n] @ c.t() / math.sqrt(L)
+            pos = torch.arange(kv - n, kv, device=x.device)[:, None]
+            sc = sc.masked_fill(torch.arange(kv, device=x.device)[None, :] > pos, float("-inf"))
+            out[at:at + n] = torch.softmax(sc, dim=-1) @ c
+            at += n
+        return (out @ self.wo.t()).to(x.dtype)
+
+
+# ------------------------------------------------------------------ a model class of another arrangement
+class ScaledCappedDecoder(DecoderModel):
+    """The embedding times a constant, and logits capped smoothly: cap * tanh(logits / cap)."""
+
+    MULT, CAP = 3.0, 4.0
+
+    def embed_tokens(self, ctx):
+        resid = super().embed_tokens(ctx)
+        resid.mul_(self.MULT)
+        return resid
+
+    def logits_at_wanted(self, stream, ctx):
+        logits = super().logits_at_wanted(stream, ctx)
+        return torch.tanh(logits / self.CAP) * self.CAP
+
+
+def test_toy_latent_cache_mixer_and_a_model_class_of_its_own():
+    register_part(LatentMixerSpec.kind, LatentMixer)
+    register_model("test_scaled_capped_decoder", ScaledCappedDecoder)
+    LAT = 24
+
+    def norm(name):
+        return RmsNormSpec(name, H, EPS)
+
+    blocks = (PreNormBlockSpec(norm("layers.0.n1.weight"), LatentMixerSpec("layers.0.mix.", H, LAT), norm("layers.0.n2.weight"),
+                               GatedMlpSpec("layers.0.mlp.", H, 56)),
+              PreNormBlockSpec(norm("layers.1.n1.weight"),
+                               AttentionSpec("layers.1.attn.", H, NQ, NKV, HD, 1.0 / math.sqrt(HD), EPS, POWER, None),
+                               norm("layers.1.n2.weight"), GatedMlpSpec("layers.1.mlp.", H, 72)))
+    spec = ModelSpec("ToyLatentForTests", V, H, blocks, (ScheduleEntry(0), ScheduleEntry(1)), norm("norm.weight"),
+                     "embed.weight", None, 4096, kind="test_scaled_capped_decoder")
+    model = build_model(spec)
+    assert type(model) is ScaledCappedDecoder
+    # two groups of pages: one array of [1, LAT] per token, and keys and values of [NKV, HD]
+    assert [n.arrays() for n in model.cache_needs] == [((1, LAT),), ((NKV, HD), (NKV, HD))]
+    w = random_tensors(model.weight_decls(), 13, sigma=0.25, dtype=torch.float32)
+    model.load(w, torch.float32, DEV)
+    runner = ModelRunner(model, 8, 20, 3, device=DEV)
+    assert [len(g.arrays) for g in runner.cache.groups] == [1, 2]
+    assert runner.cache.bytes_per_token() == (LAT + 2 * NKV * HD) * 4
+
+    def plain_model(tokens):
+        wd = {k: v.double() for k, v in w.items()}
+        T = len(tokens)
+        x = wd["embed.weight"][torch.tensor(tokens)] * ScaledCappedDecoder.MULT
+        h = plain.rms_norm(x, wd["layers.0.n1.weight"], EPS)
+        c, q = h @ wd["layers.0.mix.wc.weight"].T, h @ wd["layers.0.mix.wq.weight"].T
+        sc = (q @ c.T / math.sqrt(LAT)).masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        x = x + (torch.softmax(sc, dim=-1) @ c) @ wd["layers.0.mix.wo.weight"].T
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, wd["layers.0.n2.weight"], EPS), wd, "layers.0.mlp.")
+        p = "layers.1."
+        h = plain.rms_norm(x, wd[p + "n1.weight"], EPS)
+        qq = plain.rms_norm((h @ wd[p + "attn.q_proj.weight"].T).view(T, NQ, HD), wd[p + "attn.q_norm.weight"], EPS)
+        kk = plain.rms_norm((h @ wd[p + "attn.k_proj.weight"].T).view(T, NKV, HD), wd[p + "attn.k_norm.weight"], EPS)
+        vv = (h @ wd[p + "attn.v_proj.weight"].T).view(T, NKV, HD)
+        pos = torch.arange(T)
+        o = plain.causal_attention(plain_power_law_rotation(qq, pos, POWER), plain_power_law_rotation(kk, pos, POWER), vv,
+                                   1.0 / math.sqrt(HD), None)
+        x = x + o.reshape(T, NQ * HD) @ wd[p + "attn.o_proj.weight"].T
+        x = x + plain.swiglu_mlp(plain.rms_norm(x, wd[p + "n2.weight"], EPS), wd, p + "mlp.")
+        lg = plain.rms_norm(x, wd["norm.weight"], EPS) @ wd["embed.weight"].T
+        return torch.tanh(lg / ScaledCappedDecoder.CAP) * ScaledCappedDecoder.CAP
+
+    g = torch.Generator().manual_seed(4)
+    a = torch.randint(0, V, (50,), generator=g).tolist()
+    b = torch.randint(0, V, (31,), generator=g).tolist()
+    want_a, want_b = plain_model(a), plain_model(b)
+    got_a = [runner.step([StepEntry("a", a[:19], range(19))]).clone()]
+    lg = runner.step([StepEntry("b", b[:9], range(9)), StepEntry("a", a[19:20], (0,))]).clone()
+    got_b = [lg[:9]]
+    got_a.append(lg[9:])
+    at_a, at_b = 20, 9
+    while at_a < len(a) or at_b < len(b):
+        entries = []
+        na, nb = min(7, len(a) - at_a), min(1, len(b) - at_b)
+        if na:
+            entries.append(StepEntry("a", a[at_a:at_a + na], range(na)))
+        if nb:
+            entries.append(StepEntry("b", b[at_b:at_b + 1], (0,)))
+        lg = runner.step(entries).clone()
+        if na:
+            got_a.append(lg[:na]); lg = lg[na:]; at_a += na
+        if nb:
+            got_b.append(lg); at_b += 1
+    for got, want in ((got_a, want_a), (got_b, want_b)):
+        err = (torch.cat(got).double().cpu() - want).abs().max(dim=1).values
+        tol = 2e-5 * want.abs().max().item()
+        assert err.max().item() < tol, f"first wrong position {int((err >= tol).nonzero()[0])}: {err.max().item()}"
+    runner.end_request("a")
+    runner.end_request("b")
+    runner.cache.check()
+    assert runner.cache.free_pages() == runner.cache.total_pages()

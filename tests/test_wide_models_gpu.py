@@ -1,0 +1,82 @@
+"""The assembled engine at the layer sizes the benchmark times, against the plain model: two
+layers of Qwen3-8B's widths (hidden 4096, 32 query and 8 kv heads of 128, feed-forward 12288)
+and of Qwen3-0.6B's (hidden 1024, 16 and 8 heads of 128, so that the query width differs from
+the hidden width; feed-forward 3072; tied output), with the vocabulary cut to a few thousand
+entries (no power of two) and pages of 16.  At these widths the bfloat16 engine runs the
+gated weight-streaming product, the streaming decode attention with four (two) query heads per
+kv head and the tensor-core prefill with 32 (16) heads; the tiny models reach none of these
+shapes.  All four cuttings, float32 and bfloat16."""
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import traces
+from arle_b200.engine import ModelRunner, load_model, random_model
+from arle_b200.weights import write_random_model
+
+pytestmark = pytest.mark.gpu
+
+WIDE = {
+    "8b": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=4096, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=3001, rope_theta=1000000.0,
+               rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096, hidden_act="silu",
+               bos_token_id=0, eos_token_id=1),
+    "0.6b": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=1024, num_attention_heads=16,
+                 num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=2999, rope_theta=1000000.0,
+                 rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096, hidden_act="silu",
+                 bos_token_id=0, eos_token_id=1),
+}
+LENGTHS = [3, 70, 150, 40, 97]
+# Logits here have a spread of about 1.3, like the tiny models', but every sum is 4,096 to 12,288
+# terms long instead of 64 to 416: float32 rounding of a sum grows with the square root of its
+# length (a factor of 5 to 8), bfloat16 rounding of the activations does not (it averages out
+# over the terms).  Bounds are stated as fractions of the spread of the logits.
+REL = {torch.float32: 1e-4, torch.bfloat16: 4e-2}
+
+_made = {}
+
+
+def setup(size, tmp_path_factory):
+    if size not in _made:
+        d = str(tmp_path_factory.mktemp(f"wide{size}"))
+        write_random_model(d, WIDE[size], seed=3, sigma=0.02, gain_jitter=0.1, device="cuda")
+        cfg, w = plain.read_config(d), plain.read_weights(d)
+        reqs = traces.make_requests(cfg["vocab_size"], LENGTHS, seed=6)
+        oracle = {r: plain.forward(w, cfg, t) for r, t in reqs.items()}
+        del w
+        _made[size] = (d, reqs, oracle)
+    return _made[size]
+
+
+@pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("size", ["8b", "0.6b"])
+def test_cuttings_at_benchmark_widths(size, dtype, cut, tmp_path_factory):
+    d, reqs, oracle = setup(size, tmp_path_factory)
+    steps = traces.mixed(reqs, seed=5) if cut == "mixed" else getattr(traces, cut)(reqs)
+    model = load_model(d, dtype, "cuda")
+    runner = ModelRunner(model, 16, traces.peak_tokens(steps) // 16, 4)
+    got = traces.run_trace(runner, steps)
+    runner.cache.check()
+    assert runner.cache.free_pages() == runner.cache.total_pages()
+    from arle_b200 import ops
+    ops.check_errors("cuda")
+    for r, want in oracle.items():
+        err = (got[r].double() - want).abs().max(dim=1).values
+        tol = REL[dtype] * float(want.std())
+        bad = (err > tol).nonzero()
+        assert bad.numel() == 0, (f"{size} {cut} {dtype}: request {r} first wrong position {int(bad[0])} of {len(reqs[r])}, "
+                                  f"error {err.max().item():.3g} (allowed {tol:.3g})")
+
+
+def test_random_model_on_the_device_is_the_model_the_folder_holds(tmp_path_factory):
+    """The same configuration and seed give the same weights whether they are made on the GPU
+    (the benchmark's way) or written to a folder and loaded."""
+    d, _, _ = setup("0.6b", tmp_path_factory)
+    a = load_model(d, torch.bfloat16, "cuda")
+    b = random_model(WIDE["0.6b"], 3, torch.bfloat16, "cuda", sigma=0.02, gain_jitter=0.1)
+    assert torch.equal(a.embed, b.embed)
+    for x, y in zip(a.blocks, b.blocks):
+        assert torch.equal(x.mixer.w_qkv, y.mixer.w_qkv) and torch.equal(x.mixer.w_o, y.mixer.w_o)
+        assert torch.equal(x.mixer.q_norm, y.mixer.q_norm) and torch.equal(x.ffn.w_gate_up, y.ffn.w_gate_up)
+        assert torch.equal(x.ffn.w_down, y.ffn.w_down) and torch.equal(x.mixer_norm.weight, y.mixer_norm.weight)

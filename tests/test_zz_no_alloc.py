@@ -58,10 +58,13 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
         args = [c["logits"].data_ptr(), vocab, rows, vocab, c["temp"].data_ptr(), c["top_k"].data_ptr(),
                 c["top_p"].data_ptr(), c["min_p"].data_ptr(), c["u"].data_ptr()]
         assert lib.arle_sample(*args, scratch.data_ptr(), want.data_ptr(), stream) == 0
-        before = torch.cuda.memory_allocated()
+        # free bytes as the driver counts them: an allocation inside the call, by whatever
+        # route, would lower the figure (torch's own counters only see torch's allocator)
+        torch.cuda.synchronize()
+        before = torch.cuda.mem_get_info()[0]
         assert lib.arle_sample_static(*args, got.data_ptr(), stream) == 0
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == before
         # token ids: the same kernel on the same numbers, so equality is the tolerance
         assert got.tolist() == want.tolist()
         assert all(0 <= t < vocab for t in got.tolist())
@@ -77,11 +80,18 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     lib = _lib()
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
     rows, vocab = 8, 151936                      # 1,215,488 floats > 1,048,576
-    lg = torch.zeros(rows, vocab, device="cuda")
+    lg = torch.randn(rows, vocab, device="cuda")
     out = torch.full((rows,), 7, dtype=torch.int32, device="cuda")
-    code = lib.arle_sample_static(lg.data_ptr(), vocab, rows, vocab, None, None, None, None, None, out.data_ptr(), stream)
+    temp = torch.full((rows,), 0.9, device="cuda")
+    u = torch.full((rows,), 0.5, device="cuda")
+    code = lib.arle_sample_static(lg.data_ptr(), vocab, rows, vocab, temp.data_ptr(), None, None, None, u.data_ptr(),
+                                  out.data_ptr(), stream)
     assert code == -4
     assert b"ARLE_SAMPLE_STATIC_MAX_FLOATS" in lib.arle_no_alloc_error_string(code)
     torch.cuda.synchronize()
     assert out.tolist() == [7] * rows            # nothing was launched
+    # without temperatures every row is an argmax, which does not use the array: the same size is taken
+    assert lib.arle_sample_static(lg.data_ptr(), vocab, rows, vocab, None, None, None, None, None, out.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert out.tolist() == lg.argmax(dim=1).tolist()
     assert lib.arle_sample_static(lg.data_ptr(), vocab - 1, 1, vocab, None, None, None, None, None, out.data_ptr(), stream) == -3

@@ -43,6 +43,12 @@ INIT = {"A": dict(sigma=0.02, gain_jitter=0.1), "B": dict(sigma=0.03, gain_jitte
         "F": dict(sigma=0.03, gain_jitter=0.2)}
 CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
 PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 16, "E": 16, "F": 16}
+# With small weights a tied model repeats one token for ever, and a test of generation that
+# compares such outputs passes for any decode path that gets the first token right.  The
+# generation tests therefore use weights large enough that the greedy continuation keeps
+# changing, and check that it does (``assert_varied``).
+VARIED_INIT = {"A": dict(sigma=0.15), "B": dict(sigma=0.1), "C": dict(sigma=0.15), "D": dict(sigma=0.15),
+               "E": dict(sigma=0.06), "F": dict(sigma=0.08)}
 
 
 def make_model_dir(name: str, seed: int = 0, root: str = None, **init) -> str:
@@ -51,3 +57,14 @@ def make_model_dir(name: str, seed: int = 0, root: str = None, **init) -> str:
     kw = dict(INIT[name])
     kw.update(init)
     return write_random_model(os.path.join(root, name), CONFIGS[name], seed, **kw)
+
+
+def make_varied_model_dir(name: str, seed: int = 0, root: str = None) -> str:
+    """Like ``make_model_dir`` with the larger weights of ``VARIED_INIT``."""
+    return make_model_dir(name, seed, root, **VARIED_INIT[name])
+
+
+def assert_varied(sequences, least: int = 4) -> None:
+    """Every reference continuation must hold at least ``least`` different tokens."""
+    for s in sequences:
+        assert len(set(s)) >= min(least, len(s)), f"reference continuation {s} is too uniform to test anything"

@@ -86,6 +86,40 @@ def mixed(requests, seed: int = 0, max_live: int = 4, tail: int = 8) -> list:
     return steps
 
 
+def preempted(requests, victim: str = None, tail: int = 6) -> list:
+    """Every request runs as a portion and then token by token, up to three at a time; the
+    ``victim`` (the longest request by default) is ended half-way through, its pages go to the
+    others, and later it starts again from its first token under the same name, as a scheduler
+    that preempts by recomputation would have it.  Logits are wanted everywhere, so the victim's
+    early positions come out twice."""
+    names = list(requests)
+    victim = victim or max(names, key=lambda r: len(requests[r]))
+    steps = []
+
+    def run(rids, stop_victim_at=None):
+        upto = {r: 0 for r in rids}
+        live = list(rids)
+        while live:
+            entries, end = [], []
+            for r in list(live):
+                t, at = requests[r], upto[r]
+                left = len(t) - at
+                n = 1 if left <= tail or at > 0 and left <= tail + 3 else max(2, min(left - tail, 11 if at else left - tail))
+                entries.append(_entry(r, t[at:at + n]))
+                upto[r] = at + n
+                if upto[r] == len(t) or (r == victim and stop_victim_at is not None and upto[r] >= stop_victim_at):
+                    end.append(r)
+                    live.remove(r)
+            steps.append(_step(len(steps), entries, end))
+
+    first = [r for r in names if r != victim][:2]
+    run([victim] + first, stop_victim_at=max(2, len(requests[victim]) // 2))
+    rest = [r for r in names if r != victim and r not in first]
+    run(rest[:1] + [victim] + rest[1:2])
+    run(rest[2:])
+    return steps
+
+
 def peak_tokens(steps, round_to: int = 64) -> int:
     """The most tokens live requests hold at any time, each request's count
     rounded up to a multiple of ``round_to`` (the replay tool's --max-tokens)."""
@@ -115,3 +149,23 @@ def run_trace(runner, steps) -> Dict[str, torch.Tensor]:
         for r in s["end"]:
             runner.end_request(r)
     return {r: torch.cat(v) for r, v in got.items()}
+
+
+def run_trace_by_position(runner, steps) -> list:
+    """Like ``run_trace`` for traces in which a request may start again after it ended:
+    returns (request, position, logits row) for every wanted place, in the order they came."""
+    out, held = [], {}
+    for s in steps:
+        entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]]
+        logits = runner.step(entries)
+        at = 0
+        for e in s["entries"]:
+            base = held.get(e["id"], 0)
+            for k, w in enumerate(e["want"]):
+                out.append((e["id"], base + w, logits[at + k].detach().float().cpu().clone()))
+            at += len(e["want"])
+            held[e["id"]] = base + len(e["tokens"])
+        for r in s["end"]:
+            runner.end_request(r)
+            held.pop(r, None)
+    return out
