@@ -13,6 +13,7 @@ infer/src/model.rs:502-510, :664-701) with constraints between them
 """
 from __future__ import annotations
 
+import gc
 from typing import List, Optional, Sequence
 
 import torch
@@ -156,6 +157,12 @@ class _DecodeGraph:
             with ops.use_kernel_set(self.runner.kernel_set):
                 model.forward(ctx)
                 torch.cuda.synchronize(self.runner.device)
+                # No graph may be destroyed while a stream captures (it invalidates the capture):
+                # collect what is garbage now, an earlier engine's graphs for one, and keep the
+                # collector from running until the capture has ended.
+                gc.collect()
+                gc_was_on = gc.isenabled()
+                gc.disable()
                 self.ws.frozen = True
                 try:
                     before = ops.launch_count()
@@ -165,6 +172,8 @@ class _DecodeGraph:
                     self.launches = ops.launch_count() - before
                 finally:
                     self.ws.frozen = False
+                    if gc_was_on:
+                        gc.enable()
             self.graph = graph
             self.generation = self.ws.generation
             return ctx, self.logits

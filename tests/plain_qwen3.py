@@ -95,7 +95,21 @@ def rope_half_split(x: torch.Tensor, positions: torch.Tensor, theta: float) -> t
     return torch.cat([lo * cos - hi * sin, lo * sin + hi * cos], dim=-1)
 
 
-def causal_attention(q, k, v, scale: float, window=None) -> torch.Tensor:
+def _same(x):
+    return x
+
+
+def bf16_round(x: torch.Tensor) -> torch.Tensor:
+    """x rounded to bfloat16 (nearest even) and widened again.  Passed as ``rnd`` to the functions
+    below it marks the places where a bfloat16 engine stores an activation in 16 bits (outputs
+    of norms, projections, the gate and attention, and the attention probabilities before P.V,
+    crates/cuda-kernels/tools/tilelang/batch_prefill_paged_hd128.py:213-232), so that the
+    size of bfloat16 rounding at a given width can be measured instead of guessed.  The
+    residual stays unrounded, as in the engine."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
+def causal_attention(q, k, v, scale: float, window=None, rnd=_same) -> torch.Tensor:
     """q: [T, nq, hd]; k, v: [T, nkv, hd]; query head h reads kv head h // (nq/nkv).
     s_tj = (q_t . k_j) * scale, keys j <= t (and j > t - window when a window is
     given), softmax over j, o_t = sum_j p_tj v_j.
@@ -114,11 +128,16 @@ def causal_attention(q, k, v, scale: float, window=None) -> torch.Tensor:
         s = (q[:, h, :] @ k[:, h // g, :].T) * scale
         s = s.masked_fill(~mask, float("-inf"))
         p = torch.softmax(s, dim=-1)
-        out[:, h, :] = p @ v[:, h // g, :]
+        if rnd is not _same:
+            # the kernels round the unnormalised exp(s - max) and divide by the unrounded sum afterwards
+            e = torch.exp(s - s.max(dim=-1, keepdim=True).values)
+            out[:, h, :] = (rnd(e) @ v[:, h // g, :]) / e.sum(dim=-1, keepdim=True)
+        else:
+            out[:, h, :] = p @ v[:, h // g, :]
     return out
 
 
-def attention_mixer(x, w: dict, pre: str, cfg: dict, positions, window=None, shared_kv=None):
+def attention_mixer(x, w: dict, pre: str, cfg: dict, positions, window=None, shared_kv=None, rnd=_same):
     """q/k/v projections without bias, per-head RMSNorm of q and k (one weight of
     head_dim shared by all heads, the layer's eps), rotation after the norm, V
     untouched, causal attention, output projection.  Returns the output and the
@@ -128,60 +147,61 @@ def attention_mixer(x, w: dict, pre: str, cfg: dict, positions, window=None, sha
     (o_proj); crates/train/src/qwen3.rs:90-140."""
     T = x.shape[0]
     nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
-    q = (x @ w[pre + "q_proj.weight"].T).view(T, nq, hd)
+    q = rnd(x @ w[pre + "q_proj.weight"].T).view(T, nq, hd)
     q = rms_norm(q, w[pre + "q_norm.weight"], cfg["rms_norm_eps"])
-    q = rope_half_split(q, positions, cfg["rope_theta"])
+    q = rnd(rope_half_split(q, positions, cfg["rope_theta"]))
     if shared_kv is None:
-        k = (x @ w[pre + "k_proj.weight"].T).view(T, nkv, hd)
-        v = (x @ w[pre + "v_proj.weight"].T).view(T, nkv, hd)
+        k = rnd(x @ w[pre + "k_proj.weight"].T).view(T, nkv, hd)
+        v = rnd(x @ w[pre + "v_proj.weight"].T).view(T, nkv, hd)
         k = rms_norm(k, w[pre + "k_norm.weight"], cfg["rms_norm_eps"])
-        k = rope_half_split(k, positions, cfg["rope_theta"])
+        k = rnd(rope_half_split(k, positions, cfg["rope_theta"]))
     else:
         k, v = shared_kv
-    o = causal_attention(q, k, v, 1.0 / math.sqrt(hd), window)
-    return o.reshape(T, nq * hd) @ w[pre + "o_proj.weight"].T, (k, v)
+    o = rnd(causal_attention(q, k, v, 1.0 / math.sqrt(hd), window, rnd))
+    return rnd(o.reshape(T, nq * hd) @ w[pre + "o_proj.weight"].T), (k, v)
 
 
-def swiglu_mlp(x, w: dict, pre: str) -> torch.Tensor:
+def swiglu_mlp(x, w: dict, pre: str, rnd=_same) -> torch.Tensor:
     """d = (silu(x Wg^T) * (x Wu^T)) Wd^T, silu(g) = g / (1 + exp(-g)); no bias.
     infer/src/model/qwen3/prefill.rs:291-337;
     crates/cuda-kernels/csrc/misc/elementwise_basic.cu:18-24."""
-    g = x @ w[pre + "gate_proj.weight"].T
-    u = x @ w[pre + "up_proj.weight"].T
-    return (g / (1.0 + torch.exp(-g)) * u) @ w[pre + "down_proj.weight"].T
+    g = rnd(x @ w[pre + "gate_proj.weight"].T)
+    u = rnd(x @ w[pre + "up_proj.weight"].T)
+    return rnd(rnd(g / (1.0 + torch.exp(-g)) * u) @ w[pre + "down_proj.weight"].T)
 
 
-def decoder_block(x, w: dict, layer: int, cfg: dict, positions, window=None, shared_kv=None):
+def decoder_block(x, w: dict, layer: int, cfg: dict, positions, window=None, shared_kv=None, rnd=_same):
     """Pre-norm block: x1 = x + attn(norm(x)); x2 = x1 + mlp(norm(x1)).  Returns
     x2 and the block's (k, v).
     infer/src/model/qwen3/prefill.rs:618-776 (norm :644, add :737, norm :746,
     add :766)."""
     p = f"model.layers.{layer}."
     eps = cfg["rms_norm_eps"]
-    h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-    a, kv = attention_mixer(h, w, p + "self_attn.", cfg, positions, window, shared_kv)
+    h = rnd(rms_norm(x, w[p + "input_layernorm.weight"], eps))
+    a, kv = attention_mixer(h, w, p + "self_attn.", cfg, positions, window, shared_kv, rnd)
     x = x + a
-    h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
-    return x + swiglu_mlp(h, w, p + "mlp."), kv
+    h = rnd(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps))
+    return x + swiglu_mlp(h, w, p + "mlp.", rnd), kv
 
 
-def output_logits(x, w: dict, cfg: dict) -> torch.Tensor:
+def output_logits(x, w: dict, cfg: dict, rnd=_same) -> torch.Tensor:
     """Final RMSNorm then projection with lm_head.weight, or with the embedding
     table when tie_word_embeddings; no bias and no scaling of the logits.
     infer/src/model/qwen3/prefill.rs:426-455; infer/src/model/qwen3/weights.rs:305-316."""
-    f = rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+    f = rnd(rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"]))
     head = w["model.embed_tokens.weight"] if cfg["tie_word_embeddings"] else w["lm_head.weight"]
     return f @ head.T
 
 
-def forward(w: dict, cfg: dict, tokens, schedule=None) -> torch.Tensor:
+def forward(w: dict, cfg: dict, tokens, schedule=None, rnd=_same) -> torch.Tensor:
     """Logits [T, vocab] for one whole sequence starting at position 0.
 
     ``schedule`` lists the layers in running order as (layer, keys_of) pairs:
     ``keys_of`` is None when the entry computes its own keys and values, or the
     index of an earlier entry whose keys and values it attends over instead.
     The default runs layers 0..L-1 once each.  Only the default is a Qwen3
-    model; other lists exist for the tests of the engine's layer schedule."""
+    model; other lists exist for the tests of the engine's layer schedule.
+    ``rnd=bf16_round`` rounds every stored activation to bfloat16 (see there)."""
     ids = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(ids.numel())
     x = embedding(w["model.embed_tokens.weight"], ids)
@@ -190,9 +210,9 @@ def forward(w: dict, cfg: dict, tokens, schedule=None) -> torch.Tensor:
     kvs = []
     for layer, keys_of in order:
         shared = kvs[keys_of] if keys_of is not None else None
-        x, kv = decoder_block(x, w, layer, cfg, positions, wins[layer], shared)
+        x, kv = decoder_block(x, w, layer, cfg, positions, wins[layer], shared, rnd)
         kvs.append(kv)
-    return output_logits(x, w, cfg)
+    return output_logits(x, w, cfg, rnd)
 
 
 # --------------------------------------------------------------------- sampling

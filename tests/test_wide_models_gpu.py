@@ -28,10 +28,13 @@ WIDE = {
 }
 LENGTHS = [3, 70, 150, 40, 97]
 # Logits here have a spread of about 1.3, like the tiny models', but every sum is 4,096 to 12,288
-# terms long instead of 64 to 416: float32 rounding of a sum grows with the square root of its
-# length (a factor of 5 to 8), bfloat16 rounding of the activations does not (it averages out
-# over the terms).  Bounds are stated as fractions of the spread of the logits.
-REL = {torch.float32: 1e-4, torch.bfloat16: 4e-2}
+# terms long instead of 64 to 416, and float32 rounding of a sum grows with the square root of its
+# length (a factor of 5 to 8): the float32 bound is 1e-4 of the spread of the logits.  What
+# bfloat16 storage of the activations costs at these widths is measured, not guessed: the plain
+# model is run once more with every stored activation rounded to bfloat16 (``plain.bf16_round``),
+# and the engine may be one and a half times as far from the exact logits as that run is at its
+# worst (measured: 1.0 to 1.2 times).
+REL_F32 = 1e-4
 
 _made = {}
 
@@ -43,8 +46,9 @@ def setup(size, tmp_path_factory):
         cfg, w = plain.read_config(d), plain.read_weights(d)
         reqs = traces.make_requests(cfg["vocab_size"], LENGTHS, seed=6)
         oracle = {r: plain.forward(w, cfg, t) for r, t in reqs.items()}
+        rounded = max((plain.forward(w, cfg, t, rnd=plain.bf16_round) - oracle[r]).abs().max().item() for r, t in reqs.items())
         del w
-        _made[size] = (d, reqs, oracle)
+        _made[size] = (d, reqs, oracle, rounded)
     return _made[size]
 
 
@@ -52,7 +56,7 @@ def setup(size, tmp_path_factory):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 @pytest.mark.parametrize("size", ["8b", "0.6b"])
 def test_cuttings_at_benchmark_widths(size, dtype, cut, tmp_path_factory):
-    d, reqs, oracle = setup(size, tmp_path_factory)
+    d, reqs, oracle, rounded = setup(size, tmp_path_factory)
     steps = traces.mixed(reqs, seed=5) if cut == "mixed" else getattr(traces, cut)(reqs)
     model = load_model(d, dtype, "cuda")
     runner = ModelRunner(model, 16, traces.peak_tokens(steps) // 16, 4)
@@ -63,16 +67,16 @@ def test_cuttings_at_benchmark_widths(size, dtype, cut, tmp_path_factory):
     ops.check_errors("cuda")
     for r, want in oracle.items():
         err = (got[r].double() - want).abs().max(dim=1).values
-        tol = REL[dtype] * float(want.std())
+        tol = REL_F32 * float(want.std()) if dtype == torch.float32 else 1.5 * rounded
         bad = (err > tol).nonzero()
         assert bad.numel() == 0, (f"{size} {cut} {dtype}: request {r} first wrong position {int(bad[0])} of {len(reqs[r])}, "
-                                  f"error {err.max().item():.3g} (allowed {tol:.3g})")
+                                  f"error {err.max().item():.3g} (allowed {tol:.3g}; logits spread {float(want.std()):.3g})")
 
 
 def test_random_model_on_the_device_is_the_model_the_folder_holds(tmp_path_factory):
     """The same configuration and seed give the same weights whether they are made on the GPU
     (the benchmark's way) or written to a folder and loaded."""
-    d, _, _ = setup("0.6b", tmp_path_factory)
+    d = setup("0.6b", tmp_path_factory)[0]
     a = load_model(d, torch.bfloat16, "cuda")
     b = random_model(WIDE["0.6b"], 3, torch.bfloat16, "cuda", sigma=0.02, gain_jitter=0.1)
     assert torch.equal(a.embed, b.embed)
