@@ -55,6 +55,7 @@ _SIGNATURES = {
     "arle_gemm_plain_bf16": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "arle_gemm_skinny": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_gemm_skinny_gated": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
+    "arle_gemm_skinny_fused": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _F, _F, _P, _I, _P, _P, _I, _P, _P, _P],
     "arle_gemm_tcgen05": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, _P],
     "arle_argmax": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "arle_scatter_tokens": [_P, _P, _P, _I, _P],
@@ -246,8 +247,96 @@ def residual_add(resid, delta) -> None:
 
 
 # ------------------------------------------------------------------------ gemm
-def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, N] = x[M, K] . w[N, K]^T (weights stored [out_features, in_features])."""
+SS_TABLE_SHAPE = (16, 192)          # a sum-of-squares table of the fused products: [rows, slots], float32
+
+
+class ResidualSink:
+    """Where a product's result goes instead of an output tensor, so that the norm that follows
+    needs no kernel: the sums are added into ``resid`` (float32 [M, N], in place), ``xs`` gets
+    bfloat16(resid * gamma) (the norm's output without its per-row factor) and ``ss`` (float32
+    ``SS_TABLE_SHAPE``) the sums of squares of the new residual rows, spread over slots that the
+    reader adds up.  ``eps`` travels with it to the reader."""
+
+    def __init__(self, resid, gamma, eps, xs, ss):
+        self.resid, self.gamma, self.eps, self.xs, self.ss = resid, gamma, float(eps), xs, ss
+        self.filled = False
+
+
+class ScaledRows:
+    """Rows that still lack the per-row factor of their RMSNorm: the normalised rows are
+    ``rows[m] * rsqrt(sum(ss[m, :]) / rows.shape[1] + eps)``.  A product over such rows applies
+    the factor to its sums (``gemm(..., row_scale=...)``)."""
+
+    def __init__(self, rows, ss, eps):
+        self.rows, self.ss, self.eps = rows, ss, float(eps)
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+
+def fused_gemm_supported(x, w) -> bool:
+    """The fusions live in the weight-streaming kernel: bfloat16, up to 8 rows, its alignment rules,
+    and the fast kernel set."""
+    return (_KERNEL_SET == "fast" and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and x.shape[0] <= 8 and x.shape[1] % 32 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def fused_gemm_shape_ok(rows: int, w: torch.Tensor, gated: bool = False) -> bool:
+    """Whether a product of ``rows`` bfloat16 rows with ``w`` can take the fused kernel (asked by the
+    parts before they hand out a sink or rows without their norm factor)."""
+    return (_KERNEL_SET == "fast" and w is not None and w.is_cuda and w.dtype == torch.bfloat16 and 0 < rows <= 8
+            and w.shape[1] % 32 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and w.data_ptr() % 16 == 0
+            and (not gated or gated_gemm_fits(w.shape[1])))
+
+
+def _fused_gemm(x, w, out, gated: bool, scaled: "ScaledRows", sink: "ResidualSink") -> None:
+    M, K = x.shape
+    N = w.shape[0]
+    in_ss = inv_w = eps = None
+    if scaled is not None:
+        if scaled.ss.dtype != torch.float32 or tuple(scaled.ss.shape) != SS_TABLE_SHAPE or not scaled.ss.is_contiguous():
+            raise KernelError("gemm: a row-scale table must be contiguous float32 of SS_TABLE_SHAPE")
+        in_ss, inv_w, eps = scaled.ss, 1.0 / K, scaled.eps
+    if sink is not None:
+        r, xs = sink.resid, sink.xs
+        if (r.dtype != torch.float32 or tuple(r.shape) != (M, N) or r.stride(1) != 1 or xs.dtype != torch.bfloat16
+                or tuple(xs.shape) != (M, N) or xs.stride(1) != 1 or sink.gamma.dtype != torch.float32
+                or sink.gamma.numel() != N or tuple(sink.ss.shape) != SS_TABLE_SHAPE or sink.ss.dtype != torch.float32):
+            raise KernelError("gemm: residual sink does not fit the product")
+    _check(library().arle_gemm_skinny_fused(
+        _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out) if out is not None else 1,
+        out.stride(0) if out is not None else 0, M, N, K, int(gated), _ptr(in_ss), float(inv_w or 0.0), float(eps or 0.0),
+        _ptr(sink.resid) if sink else None, sink.resid.stride(0) if sink else 0, _ptr(sink.gamma) if sink else None,
+        _ptr(sink.xs) if sink else None, sink.xs.stride(0) if sink else 0, _ptr(sink.ss) if sink else None,
+        _ptr(error_flag(x.device)), _stream()), "gemm_skinny_fused")
+    if sink is not None:
+        sink.filled = True
+
+
+def gemm(x, w: torch.Tensor, out: torch.Tensor, sink: "ResidualSink" = None) -> bool:
+    """out[M, N] = x[M, K] . w[N, K]^T (weights stored [out_features, in_features]).
+
+    ``x`` may be ``ScaledRows`` (the product then applies their per-row factor).  With a ``sink`` the
+    result is added into the residual instead (see ``ResidualSink``) when the shapes allow the fused
+    kernel; the return value says whether that happened (if not, ``out`` holds the product as
+    usual and the sink is untouched)."""
+    scaled = x if isinstance(x, ScaledRows) else None
+    if scaled is not None:
+        x = scaled.rows
+    if scaled is not None or sink is not None:
+        if fused_gemm_supported(x, w) and w.shape[1] == x.shape[1]:
+            use_sink = sink is not None
+            _fused_gemm(x, w, None if use_sink else out, False, scaled, sink)
+            return use_sink
+        if scaled is not None:
+            raise KernelError("gemm: rows that lack their norm factor need the fused weight-streaming kernel "
+                              f"(bfloat16, up to 8 rows, K a multiple of 32); got x {tuple(x.shape)} {x.dtype}")
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
@@ -257,7 +346,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
             raise KernelError("gemm: the float32 path takes float32 activations with unit inner stride")
         _check(library().arle_gemm_f32(_ptr(x), _ptr(w), _dt(w), _ptr(out), M, N, K, x.stride(0), w.stride(0),
                                        out.stride(0), _stream()), "gemm_f32")
-        return
+        return False
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm: bfloat16 path needs bfloat16 operands, got {x.dtype} and {w.dtype}")
     _ptr(x), _ptr(w), _ptr(out)
@@ -266,20 +355,21 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
             raise KernelError("gemm: operands need unit inner strides")
         _check(library().arle_gemm_plain_bf16(_ptr(x), _ptr(w), _ptr(out), _dt(out), M, N, K, x.stride(0), w.stride(0),
                                               out.stride(0), _stream()), "gemm_plain_bf16")
-        return
+        return False
     if skinny_gemm_supported(x, w, out):
         _check(library().arle_gemm_skinny(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(out), _dt(out), out.stride(0),
                                           M, N, K, _ptr(error_flag(x.device)), _stream()), "gemm_skinny")
-        return
+        return False
     if M >= _TCGEN05_MIN_ROWS and tcgen05_gemm_supported(x, w, out):
         gemm_tcgen05(x, w, out)
-        return
+        return False
     if out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     elif out.dtype == torch.float32:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
         raise KernelError(f"gemm: output type {out.dtype}")
+    return False
 
 
 _TCGEN05_MIN_ROWS = 1 << 30
@@ -525,6 +615,11 @@ def gemm_silu_mul(x: torch.Tensor, w: torch.Tensor, gate_up: torch.Tensor, out: 
     T, I = out.shape
     if w.shape[0] != 2 * I or gate_up.shape != (T, 2 * I):
         raise KernelError(f"gemm_silu_mul: shapes w {tuple(w.shape)} gate_up {tuple(gate_up.shape)} out {tuple(out.shape)}")
+    if isinstance(x, ScaledRows):
+        if not (fused_gemm_supported(x.rows, w) and gated_gemm_fits(x.rows.shape[1]) and out.stride(1) == 1):
+            raise KernelError("gemm_silu_mul: rows that lack their norm factor need the gated weight-streaming kernel")
+        _fused_gemm(x.rows, w, out, True, x, None)
+        return
     if (_KERNEL_SET == "fast" and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and skinny_gemm_supported(x, w, out) and gated_gemm_fits(x.shape[1])):
         _ptr(x), _ptr(w), _ptr(out)
@@ -538,9 +633,9 @@ def gemm_silu_mul(x: torch.Tensor, w: torch.Tensor, gate_up: torch.Tensor, out: 
 
 def gated_gemm_fits(K: int) -> bool:
     """The gate needs whole sums in one CTA: 8 rows of x (K + 8 elements each) must fit in
-    shared memory beside the kernel's ring of four 32 KB stages and its reduction scratch
-    (about 146 KB of the 227 KB): K up to about 5,200."""
-    return 16 * (K + 8) <= 83000
+    shared memory beside the kernel's ring of four 32 KB stages, its reduction scratch and
+    the staged table of row factors (about 147 KB of the 227 KB): K up to about 5,300."""
+    return 16 * (K + 8) <= 85600
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:

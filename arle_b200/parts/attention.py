@@ -82,8 +82,14 @@ class Attention(Mixer):
     def cache_need(self):
         return CacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
+    def takes_scaled_rows(self, num_rows):
+        return ops.fused_gemm_shape_ok(num_rows, self.w_qkv)
+
+    def can_sink(self, num_rows):
+        return ops.fused_gemm_shape_ok(num_rows, self.w_o)
+
     # ---------------------------------------------------------------- forward
-    def forward(self, x, ctx, cache, state):
+    def forward(self, x, ctx, cache, state, sink=None):
         s = self.spec
         T = x.shape[0]
         nq, nkv, hd = s.num_heads, s.num_kv_heads, s.head_dim
@@ -104,7 +110,8 @@ class Attention(Mixer):
         ops.paged_attention(qkv[:, : nq * hd], attn, cache.k, cache.v, ctx.positions, ctx.row_of_token,
                             cache.block_table, nq, nkv, hd, cache.page_size, s.scale, s.window, batch=ctx)
         out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)
-        ops.gemm(attn, self.w_o, out)
+        if ops.gemm(attn, self.w_o, out, sink=sink):
+            return None                       # summed into the residual by the product itself
         return out
 
 

@@ -105,6 +105,17 @@ class Part:
         engine uses to leave memory for them beside the cache)."""
         return 0
 
+    # Optional fusion of the norms into the products around them (decode steps of few rows; see
+    # ``ops.ResidualSink`` and ``ops.ScaledRows``).  A part that says yes to ``takes_scaled_rows`` may
+    # get ``ops.ScaledRows`` as its input instead of a tensor; a part that says yes to ``can_sink`` may
+    # be called with ``sink=`` and, if it gave the sink to its last product, returns None instead of
+    # its output.  Parts that know nothing of this are never asked to.
+    def takes_scaled_rows(self, num_rows: int) -> bool:
+        return False
+
+    def can_sink(self, num_rows: int) -> bool:
+        return False
+
 
 class Norm(Part):
     """y = norm(x) over the last axis.  ``forward(stream, ...)`` is driven by the
@@ -113,6 +124,11 @@ class Norm(Part):
 
     eps: float
     weight: torch.Tensor
+
+    def deferred(self):
+        """(gain float32 [width], eps) when the norm is x * rsqrt(mean(x^2) + eps) * gain, so that its
+        per-row factor can be applied after a product instead of before it; None otherwise."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -153,3 +169,9 @@ class Block(Part):
 
     def forward(self, stream, ctx, cache, state) -> None:
         raise NotImplementedError
+
+    def entry(self):
+        """(the norm this block applies first, the part that reads its output), or None: lets the
+        block that runs before this one fold its last residual sum and this norm into its last
+        product."""
+        return None

@@ -45,11 +45,26 @@ class PreNormBlock(Block):
         return (self.mixer_norm.scratch_elements_per_token() + self.ffn_norm.scratch_elements_per_token()
                 + max(self.mixer.scratch_elements_per_token(), self.ffn.scratch_elements_per_token()))
 
+    def entry(self):
+        return self.mixer_norm, self.mixer
+
     def forward(self, stream, ctx, cache, state):
+        T = ctx.num_tokens
         h = stream.normed(self.mixer_norm, "normed_a")
-        stream.add(self.mixer.forward(h, ctx, cache, state))
+        # where a branch's last product can add into the residual and leave the next norm's input behind,
+        # and that norm's reader can apply the norm's factor itself, the norm between them is no kernel
+        sink = stream.sink_for(self.ffn_norm, self.ffn, "normed_b") if self.mixer.can_sink(T) else None
+        if sink is not None:
+            stream.add(self.mixer.forward(h, ctx, cache, state, sink=sink))
+        else:
+            stream.add(self.mixer.forward(h, ctx, cache, state))
         h = stream.normed(self.ffn_norm, "normed_b")
-        stream.add(self.ffn.forward(h, ctx))
+        nxt = stream.next_entry
+        sink = stream.sink_for(nxt[0], nxt[1], "normed_a") if nxt is not None and self.ffn.can_sink(T) else None
+        if sink is not None:
+            stream.add(self.ffn.forward(h, ctx, sink=sink))
+        else:
+            stream.add(self.ffn.forward(h, ctx))
 
 
 register_part(PreNormBlockSpec.kind, PreNormBlock)

@@ -51,14 +51,21 @@ class GatedMlp(FeedForward):
     def scratch_elements_per_token(self):
         return 3 * self.spec.intermediate_size + self.spec.hidden_size
 
-    def forward(self, x, ctx):
+    def takes_scaled_rows(self, num_rows):
+        return ops.fused_gemm_shape_ok(num_rows, self.w_gate_up, gated=True)
+
+    def can_sink(self, num_rows):
+        return ops.fused_gemm_shape_ok(num_rows, self.w_down)
+
+    def forward(self, x, ctx, sink=None):
         s = self.spec
         T = x.shape[0]
         gu = ctx.ws.get("gate_up", (T, 2 * s.intermediate_size), x.dtype)
         act = ctx.ws.get("ffn_act", (T, s.intermediate_size), x.dtype)
         ops.gemm_silu_mul(x, self.w_gate_up, gu, act)
         out = ctx.ws.get("ffn_out", (T, s.hidden_size), x.dtype)
-        ops.gemm(act, self.w_down, out)
+        if ops.gemm(act, self.w_down, out, sink=sink):
+            return None                       # summed into the residual by the product itself
         return out
 
 

@@ -23,20 +23,57 @@ class ResidualStream:
 
     ``add(delta)`` only remembers the branch output; the next ``normed(...)`` sums
     it into the residual and normalises in one kernel.  Two ``add`` calls in a row
-    (a block with parallel branches) are summed right away."""
+    (a block with parallel branches) are summed right away.
+
+    For steps of few rows the norm kernel can disappear altogether: ``sink_for(norm, ...)``
+    hands out an ``ops.ResidualSink`` that a branch's last product fills (residual sum, the norm's
+    gain, sums of squares), and the ``normed(...)`` of that norm then returns ``ops.ScaledRows``, whose
+    per-row factor the next product applies.  ``next_entry`` is what runs after the current block
+    (its first norm and that norm's reader), set by the model."""
 
     def __init__(self, resid: torch.Tensor, ws, act_dtype: torch.dtype):
         self.resid = resid
         self.ws = ws
         self.act_dtype = act_dtype
         self.pending: Optional[torch.Tensor] = None
+        self.next_entry = None
+        self._sink = None
+        self._sinks_made = 0
 
-    def add(self, delta: torch.Tensor) -> None:
+    def add(self, delta: Optional[torch.Tensor]) -> None:
+        """``delta`` None: the branch has already put its output into the residual (through a sink)."""
+        if delta is None:
+            return
         if self.pending is not None:
             ops.residual_add(self.resid, self.pending)
         self.pending = delta
 
-    def normed(self, norm, buffer_name: str) -> torch.Tensor:
+    def sink_for(self, norm, reader, buffer_name: str):
+        """A sink for the branch that runs now, if the norm that follows it can be deferred and its
+        reader takes rows without their factor; else None."""
+        T = self.resid.shape[0]
+        if (norm is None or reader is None or self.pending is not None or self.act_dtype != torch.bfloat16
+                or not self.resid.is_cuda or ops.kernel_set() != "fast" or not reader.takes_scaled_rows(T)):
+            return None
+        d = norm.deferred()
+        if d is None:
+            return None
+        gain, eps = d
+        xs = self.ws.get(buffer_name, tuple(self.resid.shape), self.act_dtype)
+        # two tables in turn: the one being filled is never the one the running product reads
+        ss = self.ws.get(f"row_ss_{self._sinks_made & 1}", ops.SS_TABLE_SHAPE, torch.float32)
+        self._sinks_made += 1
+        self._sink = (norm, ops.ResidualSink(self.resid, gain, eps, xs, ss))
+        return self._sink[1]
+
+    def normed(self, norm, buffer_name: str):
+        if self._sink is not None:
+            for_norm, sink = self._sink
+            self._sink = None
+            if sink.filled:
+                if for_norm is not norm or self.pending is not None:
+                    raise RuntimeError("a residual sink was filled for another norm than the one that runs next")
+                return ops.ScaledRows(sink.xs, sink.ss, sink.eps)
         out = self.ws.get(buffer_name, tuple(self.resid.shape), self.act_dtype)
         norm.apply(self.resid, self.pending, None, out, write_resid=self.pending is not None)
         self.pending = None
@@ -137,7 +174,9 @@ class DecoderModel:
         return resid
 
     def run_blocks(self, stream: ResidualStream, ctx) -> None:
-        for i, e in enumerate(self.spec.schedule):
+        order = self.spec.schedule
+        for i, e in enumerate(order):
+            stream.next_entry = self.blocks[order[i + 1].block].entry() if i + 1 < len(order) else None
             cl = self.entry_cache_layer[i]
             cache = ctx.cache_view(cl, writable=e.keys_of is None) if cl is not None else None
             st = ctx.state_view(self.entry_state[i]) if self.entry_state[i] is not None else None

@@ -38,6 +38,9 @@ class RmsNorm(Norm):
     def scratch_elements_per_token(self):
         return self.spec.size
 
+    def deferred(self):
+        return self.weight, self.eps
+
     def apply(self, resid, delta, rows, out, write_resid: bool):
         """out = norm(resid (+ delta)) on all rows or on ``rows``; see ops.rmsnorm."""
         ops.rmsnorm(resid, delta, rows, self.weight, self.eps, out, write_resid)

@@ -27,7 +27,7 @@ sys.path.insert(0, ROOT)
 QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
                 num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936, rope_theta=1e6,
                 rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu")
-# the other two sizes that BASELINE.json names, for runs beside the default one
+# two more sizes of the same architecture (Qwen3-0.6B and Qwen3-32B), for runs beside the default one
 QWEN3_0_6B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
                   intermediate_size=3072, tie_word_embeddings=True)
 QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,

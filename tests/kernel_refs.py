@@ -39,8 +39,14 @@ def residual_add(resid, delta):
     resid += delta.to(F32)
 
 
-def gemm(x, w, out):
+def gemm(x, w, out, sink=None):
+    """``sink`` is never taken here (the parts are told so by ``fused_gemm_shape_ok``): False."""
     out.copy_((x.to(F32) @ w.to(F32).t()).to(out.dtype))
+    return False
+
+
+def fused_gemm_shape_ok(rows, w, gated=False):
+    return False
 
 
 def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, k_cache, v_cache,
@@ -142,4 +148,4 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out):
         out[r] = int(hit[0]) if hit.numel() else int(torch.nonzero(p > 0)[-1])
 
 
-ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample")
+ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample")

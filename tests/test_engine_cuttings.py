@@ -39,14 +39,14 @@ def build_steps(cut, reqs):
     return getattr(traces, cut)(reqs)
 
 
-def check(name, dtype, cut, device, tmp_path_factory, page_size=None):
+def check(name, dtype, cut, device, tmp_path_factory, page_size=None, kernel_set="fast"):
     d, reqs, oracle = model_and_oracle(name, tmp_path_factory)
     steps = build_steps(cut, reqs)
     ps = page_size or PAGE_SIZES[name]
     # requests hold multiples of 64 tokens at the peak; a page size that does not divide 64 needs a page more each
     pages = traces.peak_tokens(steps) // ps if 64 % ps == 0 or ps % 64 == 0 else -(-traces.peak_tokens(steps) // ps) + 4
     model = load_model(d, dtype, device)
-    runner = ModelRunner(model, ps, pages, 4, device=device)
+    runner = ModelRunner(model, ps, pages, 4, device=device, kernel_set=kernel_set)
     got = traces.run_trace(runner, steps)
     runner.cache.check()
     assert all(g.pool.num_free == g.pool.num_pages for g in runner.cache.groups), "pages not given back"
@@ -74,6 +74,26 @@ def test_cuttings_gpu(name, dtype, cut, tmp_path_factory):
 def test_cuttings_gpu_larger_pages(name, page_size, cut, tmp_path_factory):
     """The TMA-fed attention kernels fetch keys in boxes of 16: pages of 32, 48 and 64 slots."""
     check(name, torch.bfloat16, cut, "cuda", tmp_path_factory, page_size=page_size)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cut", ["tail_decode", "mixed"])
+@pytest.mark.parametrize("name", ["D", "E", "F"])
+def test_cuttings_gpu_plain_kernel_set(name, cut, tmp_path_factory, monkeypatch):
+    """The same traces in bfloat16 on the general kernels only (plain FFMA products, general
+    attention, separate gate): none of the fast kernels may be launched, and the logits meet
+    the same bounds."""
+    from arle_b200 import ops
+    lib = ops.library()
+    called = []
+    for fast in ("arle_gemm_skinny", "arle_gemm_skinny_gated", "arle_gemm_tcgen05", "arle_paged_attention_decode_stream",
+                 "arle_paged_attention_decode", "arle_paged_attention_prefill", "arle_paged_attention_prefill_tc"):
+        real = getattr(lib, fast)
+        monkeypatch.setattr(lib, fast, lambda *a, _n=fast, _f=real: (called.append(_n), _f(*a))[1], raising=False)
+    mm = torch.mm
+    monkeypatch.setattr(torch, "mm", lambda *a, **k: (called.append("torch.mm"), mm(*a, **k))[1])
+    check(name, torch.bfloat16, cut, "cuda", tmp_path_factory, kernel_set="plain")
+    assert not called, f"the plain kernel set launched {sorted(set(called))}"
 
 
 @pytest.mark.parametrize("cut", CUTS)

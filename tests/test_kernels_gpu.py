@@ -149,6 +149,65 @@ def test_gemm_skinny_weight_streaming(M, N, K, out_dtype):
     ops.check_errors(DEV)                       # no bounded wait ran out
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 64, 32), (8, 4096, 4096), (8, 4096, 12288), (3, 992, 192), (5, 160, 320), (8, 1024, 3072),
+                                   (7, 5120, 25600), (2, 20000, 8192)])
+def test_gemm_with_residual_sink_and_row_scale(M, N, K):
+    """The two fusions that take the norm kernels out of a decode step.  A product with a sink adds its
+    sums into the float32 residual and leaves bfloat16(residual * gain) and the rows' sums of squares;
+    a product over those rows multiplies its sums by rsqrt(mean square + eps): together they equal
+    residual sum, RMSNorm and product done one after the other."""
+    eps = 1e-5
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    resid0 = rnd(M, N, dtype=torch.float32, seed=3)
+    gain = (1.0 + 0.2 * rnd(N, dtype=torch.float32, seed=4)).contiguous()
+    resid = resid0.clone()
+    xs = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ss = torch.full(ops.SS_TABLE_SHAPE, float("nan"), dtype=torch.float32, device=DEV)
+    sink = ops.ResidualSink(resid, gain, eps, xs, ss)
+    assert ops.fused_gemm_shape_ok(M, w) and ops.gemm(x, w, None, sink=sink) is True and sink.filled
+    ops.check_errors(DEV)
+    want_r = resid0.double() + x.double() @ w.double().t()
+    scale = want_r.abs().max().item()
+    assert (resid.double() - want_r).abs().max().item() <= 2e-5 * max(scale, 1.0)
+    assert (xs.double() - want_r * gain.double()).abs().max().item() <= 6e-3 * max(scale, 1.0)
+    assert not ss.isnan().any() and (ss[M:] == 0).all()
+    want_ss = (want_r * want_r).sum(dim=1)
+    assert ((ss.double().sum(dim=1)[:M] - want_ss).abs() / want_ss).max().item() < 1e-5
+    again_r, again_ss = resid0.clone(), torch.empty_like(ss)
+    ops.gemm(x, w, None, sink=ops.ResidualSink(again_r, gain, eps, torch.empty_like(xs), again_ss))
+    assert torch.equal(again_r, resid) and torch.equal(again_ss, ss)          # no atomics: the same bits every time
+    # the reader: a product over the unscaled rows equals the product over the normalised rows
+    w2 = rnd(300, N, dtype=torch.bfloat16, scale=0.05, seed=5)
+    rows = ops.ScaledRows(xs, ss, eps)
+    normed = want_r * torch.rsqrt((want_r * want_r).mean(dim=1, keepdim=True) + eps) * gain.double()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((M, 300), float("nan"), dtype=out_dtype, device=DEV)
+        assert ops.gemm(rows, w2, out) is False
+        exp = normed @ w2.double().t()
+        assert (out.double() - exp).abs().max().item() <= 1.2e-2 * max(exp.abs().max().item(), 1.0)
+    if ops.gated_gemm_fits(N):
+        w3 = rnd(2 * 150, N, dtype=torch.bfloat16, scale=0.08, seed=6)
+        act = torch.full((M, 150), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.gemm_silu_mul(rows, w3, torch.empty(M, 300, dtype=torch.bfloat16, device=DEV), act)
+        g, u = normed @ w3[0::2].double().t(), normed @ w3[1::2].double().t()
+        exp = g / (1 + torch.exp(-g)) * u
+        assert (act.double() - exp).abs().max().item() <= 2e-2 * max(exp.abs().max().item(), 1.0)
+    ops.check_errors(DEV)
+
+
+def test_a_sink_is_left_alone_when_the_shapes_do_not_allow_the_fused_kernel():
+    x, w = rnd(9, 64, dtype=torch.bfloat16, seed=1), rnd(32, 64, dtype=torch.bfloat16, seed=2)      # nine rows
+    resid = rnd(9, 32, dtype=torch.float32, seed=3)
+    keep = resid.clone()
+    sink = ops.ResidualSink(resid, torch.ones(32, device=DEV), 1e-6, torch.empty(9, 32, dtype=torch.bfloat16, device=DEV),
+                            torch.empty(ops.SS_TABLE_SHAPE, device=DEV))
+    out = torch.empty(9, 32, dtype=torch.bfloat16, device=DEV)
+    assert ops.gemm(x, w, out, sink=sink) is False and not sink.filled and torch.equal(resid, keep)
+    assert (out.double() - x.double() @ w.double().t()).abs().max().item() < 0.1
+    with pytest.raises(ops.KernelError):
+        ops.gemm(ops.ScaledRows(x, torch.zeros(ops.SS_TABLE_SHAPE, device=DEV), 1e-6), w, out)
+
+
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,I,K", [(1, 8, 32), (8, 12288, 4096), (3, 500, 192), (5, 37, 320), (8, 2050, 4096), (7, 100, 4608),
                                    (9, 64, 64), (40, 176, 96), (2, 64, 8192), (8, 300, 5120), (4, 128, 5376)])

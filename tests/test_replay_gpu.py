@@ -32,10 +32,10 @@ def setups(tmp_path_factory):
     return out
 
 
-def replay(model_dir, dtype, steps, out_dir, max_tokens):
+def replay(model_dir, dtype, steps, out_dir, max_tokens, extra=()):
     """Feeds the steps one at a time, each only after the previous 'done' line."""
     p = subprocess.Popen([os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype, "--out", out_dir,
-                          "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True,
+                          "--max-tokens", str(max_tokens), *extra], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True,
                          cwd=ROOT)
     try:
         for s in steps:
@@ -107,3 +107,22 @@ def test_replay_matches_plain_model(setups, tmp_path, name, cut, dtype):
     assert checked > 50
     if cut == "preempted":
         assert any(len(times) == 2 for rows in got.values() for times in rows.values())
+
+
+def test_replay_on_the_plain_kernel_set(setups, tmp_path):
+    """--kernels plain: the same trace on the general kernels; both runs meet the bound, and they
+    are not bit-equal in bfloat16 (the fast kernels did run in the default one)."""
+    d, cfg, reqs, oracle = setups["D"]
+    steps = with_positions(traces.mixed(reqs, seed=4))
+    clean = [{"step": s["step"], "entries": [{k: v for k, v in e.items() if k != "_pos0"} for e in s["entries"]],
+              "end": s["end"]} for s in steps]
+    outs = {}
+    for kernels in ("fast", "plain"):
+        out_dir = str(tmp_path / kernels)
+        replay(d, "bfloat16", clean, out_dir, traces.peak_tokens(steps), extra=("--kernels", kernels))
+        outs[kernels] = gather(steps, out_dir, cfg["vocab_size"])
+        for r, rows in outs[kernels].items():
+            for pos, times in rows.items():
+                assert np.abs(times[0].astype(np.float64) - oracle[r][pos].numpy()).max() <= ATOL["bfloat16"]
+    differ = sum(not np.array_equal(outs["fast"][r][p][0], outs["plain"][r][p][0]) for r in outs["fast"] for p in outs["fast"][r])
+    assert differ > 0
