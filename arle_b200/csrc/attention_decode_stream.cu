@@ -24,6 +24,13 @@
 // CTA stores an unnormalised partial (o, m, l) and the CTA that arrives last at the pair's
 // counter combines the pieces in the order of the keys (the reference's split-KV variant
 // runs a second kernel for that, :239-463).  Nothing waits for another CTA.
+// Fused preparation (optional, for steps that decode only): the kernel is given the raw projection
+// output [q heads | k heads | v heads] of every token instead of prepared queries and does what the
+// preparation kernel does for a decoded token itself: per-head RMSNorm and rotation of the pair's
+// query heads (every CTA, for the pairs it holds a piece of: a few hundred numbers), and of the
+// token's new key (the CTA that holds the pair's last tile), whose key and value it stores into the
+// cache and writes over the stale slot of the tile in shared memory before the tile is used.  One
+// launch and one pass over the projection output fewer per layer.
 // Rows whose step entry has more than one token are skipped.  The key range of a row is
 // [max(0, kv_len - window), kv_len).  Every mbarrier wait is bounded: when one runs out the
 // kernel raises the error flag, stops waiting and runs to its end.
@@ -68,13 +75,57 @@ struct Rows {
   }
 };
 
+// Fused preparation: q then points at the raw projection output of the step's tokens (row stride
+// q_row_stride, a row holds nq query heads, nkv key heads, nkv value heads).
+struct Prep {
+  int on;                       // 0: q holds prepared queries, nothing else here is used
+  const int* slot_mapping;      // [tokens] page * page_size + slot of the token's key and value
+  const float* q_weight;        // [HD] or null: no norm
+  const float* k_weight;
+  float eps;
+  const float* inv_freq;        // [HD / 2] or null: no rotation
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+};
+
+// One head of HD elements, lane l holding elements l * HD / 32 ..: RMSNorm over the head (if w), then the
+// half-split rotation by pos (if inv_freq); the same arithmetic, in the same order, as the preparation kernel.
+template <int HD>
+__device__ __forceinline__ void prep_head(const __nv_bfloat16* src, const float* w, float eps, const float* inv_freq,
+                                          float pos, int lane, __nv_bfloat16* dst) {
+  constexpr int VE = HD / 32;
+  float x[VE];
+#pragma unroll
+  for (int i = 0; i < VE; ++i) x[i] = __bfloat162float(src[lane * VE + i]);
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VE; ++i) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+    for (int i = 0; i < VE; ++i) x[i] = x[i] * inv * w[lane * VE + i];
+  }
+#pragma unroll
+  for (int i = 0; i < VE; ++i) {
+    float o = x[i];
+    if (inv_freq) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[i], 16);
+      float sn, cs;
+      sincosf(pos * inv_freq[(lane & 15) * VE + i], &sn, &cs);
+      o = lane < 16 ? x[i] * cs - other * sn : other * sn + x[i] * cs;
+    }
+    dst[lane * VE + i] = __float2bfloat16_rn(o);
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int R, int nq, int nkv,
-    int bt_width, int page_size, int ps_shift, float scale_log2, int window, int stages, int* __restrict__ err) {
+    int bt_width, int page_size, int ps_shift, float scale_log2, int window, int stages, Prep prep, int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr uint32_t OPERAND = kTile * HD * 2;            // bytes of the keys (or the values) of one stage
@@ -92,6 +143,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
   int* prefix = reinterpret_cast<int*>(mlv + kConsumerWarps * 16);          // [R + 1]
   int* kvl = prefix + R + 1;                                                // [R]
   int* tok = kvl + R;                                                       // [R]
+  __nv_bfloat16* heads = reinterpret_cast<__nv_bfloat16*>(mlv + kConsumerWarps * 16 + ((3 * R + 1 + 3) & ~3));   // [18][HD]: 16 query heads, new key, new value
   __shared__ __align__(8) uint64_t full[kMaxStages], empty[kMaxStages];
   __shared__ int abort_flag, is_last;
   __shared__ int own_row, own_first, own_k, by_pair;        // the CTA's place when pairs are shared out whole (below)
@@ -288,15 +340,31 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
 
       // the G query heads of this kv head as the A operand: rows 0..G-1 of 16, the rest zero
       uint32_t qa[HD / 16][4];
+      const bool has_last = prep.on && pair_begin + T <= u1;      // this piece holds the pair's last tile, hence the new key
+      if (prep.on) {
+        // heads 0..G-1: the pair's queries; G: the new key; G + 1: the new value (copied).  A warp a head.
+        const __nv_bfloat16* row = q + (size_t)t * q_row_stride;
+        const float pos = (float)(kv_len - 1);
+        for (int hh = warp; hh < G + (has_last ? 2 : 0); hh += kConsumerWarps) {
+          if (hh < G)
+            prep_head<HD>(row + (size_t)(kvh * G + hh) * HD, prep.q_weight, prep.eps, prep.inv_freq, pos, lane, heads + hh * HD);
+          else if (hh == G)
+            prep_head<HD>(row + (size_t)(nq + kvh) * HD, prep.k_weight, prep.eps, prep.inv_freq, pos, lane, heads + 16 * HD);
+          else
+            prep_head<HD>(row + (size_t)(nq + nkv + kvh) * HD, nullptr, 0.f, nullptr, 0.f, lane, heads + 17 * HD);
+        }
+        consumer_sync();
+      }
       {
-        const uint32_t* q0 = reinterpret_cast<const uint32_t*>(q + (size_t)t * q_row_stride + (size_t)(kvh * G + g) * HD) + tq;
+        const uint32_t* q0 = prep.on ? reinterpret_cast<const uint32_t*>(heads + (size_t)g * HD) + tq
+                                     : reinterpret_cast<const uint32_t*>(q + (size_t)t * q_row_stride + (size_t)(kvh * G + g) * HD) + tq;
         const uint32_t* q1 = q0 + 8 * HD / 2;
 #pragma unroll
         for (int s = 0; s < HD / 16; ++s) {
-          qa[s][0] = g < G ? __ldg(q0 + s * 8) : 0u;
-          qa[s][1] = g + 8 < G ? __ldg(q1 + s * 8) : 0u;
-          qa[s][2] = g < G ? __ldg(q0 + s * 8 + 4) : 0u;
-          qa[s][3] = g + 8 < G ? __ldg(q1 + s * 8 + 4) : 0u;
+          qa[s][0] = g < G ? q0[s * 8] : 0u;
+          qa[s][1] = g + 8 < G ? q1[s * 8] : 0u;
+          qa[s][2] = g < G ? q0[s * 8 + 4] : 0u;
+          qa[s][3] = g + 8 < G ? q1[s * 8 + 4] : 0u;
         }
       }
       float o[HD / 8][4];
@@ -314,6 +382,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
         if (kbeg < kv_len && kbeg + 16 > lo) {
           const uint32_t kt = ring_addr + (uint32_t)my_st * STAGE + (uint32_t)wk * BOX;
           const uint32_t vt = kt + OPERAND;
+          if (has_last && kbeg + 16 >= kv_len) {
+            // The new token's key and value: over the stale slot of this warp's block (lanes 0-15 the key's
+            // 16-byte pieces, lanes 16-31 the value's) and into the cache for the steps to come.
+            const int rr = (kv_len - 1) - kbeg;                // row of the block
+            const int j = lane & 15;
+            if (j < HD / 8) {
+              const uint4 val = *reinterpret_cast<const uint4*>(heads + (lane < 16 ? 16 : 17) * HD + j * 8);
+              const uint32_t at = (lane < 16 ? kt : vt) + (uint32_t)(j >> 3) * (16 * 128) + (uint32_t)rr * 128 +
+                                  (uint32_t)(((j & 7) ^ (rr & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(at), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
+                           : "memory");
+              const int slot = prep.slot_mapping[t];
+              if (slot >= 0) {
+                const int page = slot / page_size, off = slot - page * page_size;
+                __nv_bfloat16* cache = lane < 16 ? prep.k_cache : prep.v_cache;
+                *reinterpret_cast<uint4*>(cache + (((size_t)page * nkv + kvh) * page_size + off) * HD + j * 8) = val;
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");    // before a later copy writes the stage again
+            __syncwarp();
+          }
           // two accumulator sets, one for the even and one for the odd 16-element steps of the
           // head: half as long a chain of dependent tensor-core instructions
           float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -501,7 +590,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
 
 size_t fixed_smem(int G, int hd, int ctas, int R) {
   size_t n = (size_t)kConsumerWarps * G * hd * 4 + (size_t)kConsumerWarps * 16 * 2 * 4;
-  n += (size_t)(3 * R + 1) * 4;
+  n += (size_t)((3 * R + 1 + 3) & ~3) * 4;
+  n += (size_t)18 * hd * 2;                                  // prepared query heads, new key, new value
   return (n + 15) / 16 * 16;
 }
 
@@ -509,7 +599,7 @@ template <int HD>
 int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_row_stride, void* out,
                   const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, float* part_o,
                   float* part_ml, int* counters, int rows, int nq, int nkv, int bt_width, int page_size, float scale, int window,
-                  int ctas, int* err, cudaStream_t s) {
+                  int ctas, const Prep& prep, int* err, cudaStream_t s) {
   int ps_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (ps_shift = 0; (1 << ps_shift) < page_size; ++ps_shift) {}
@@ -535,12 +625,20 @@ int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, i
   if (e != cudaSuccess) return (int)e;
   e = launch_kernel(decode_stream_kernel<HD>, dim3(ctas), dim3(kThreads), smem, s, 1, mk, mv, (const __nv_bfloat16*)q,
                     q_row_stride, (__nv_bfloat16*)out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                    rows, nq, nkv, bt_width, page_size, ps_shift, scale * 1.4426950408889634f, window, stages, err);
+                    rows, nq, nkv, bt_width, page_size, ps_shift, scale * 1.4426950408889634f, window, stages, prep, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }
 
 }  // namespace
+
+ARLE_API int arle_paged_attention_decode_stream_prep(const void* q, int q_row_stride, void* out, const void* k_cache,
+                                                     const void* v_cache, long long cache_pages, const int* q_indptr,
+                                                     const int* kv_lens, const int* block_table, int bt_stride, int bt_width,
+                                                     float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
+                                                     int page_size, float scale, int window, int rows, int ctas, int fused,
+                                                     const int* slot_mapping, const float* q_weight, const float* k_weight,
+                                                     float eps, const float* inv_freq, int* err, cudaStream_t s);
 
 // k_cache / v_cache: [cache_pages, nkv, page_size, hd].  Scratch: part_o float32
 // [(ctas + rows * nkv) * (nq / nkv) * hd], part_ml float32 [(ctas + rows * nkv) * (nq / nkv) * 2], counters
@@ -553,7 +651,27 @@ ARLE_API int arle_paged_attention_decode_stream(const void* q, int q_row_stride,
                                                 float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
                                                 int page_size, float scale, int window, int rows, int ctas, int* err,
                                                 cudaStream_t s) {
+  return arle_paged_attention_decode_stream_prep(q, q_row_stride, out, k_cache, v_cache, cache_pages, q_indptr, kv_lens,
+                                                 block_table, bt_stride, bt_width, part_o, part_ml, counters, nq, nkv, hd,
+                                                 page_size, scale, window, rows, ctas, 0, nullptr, nullptr, nullptr, 0.f, nullptr,
+                                                 err, s);
+}
+
+// The same with the fused preparation (fused != 0): q is the raw projection output of the step's tokens
+// ([q heads | k heads | v heads] per row, stride q_row_stride), every row a decoded token at position
+// kv_len - 1; q_weight / k_weight (float32 [hd], may be null: no norm), inv_freq (float32 [hd / 2], may be null: no
+// rotation; otherwise the whole head is rotated), slot_mapping int32 [tokens].  The new keys and values are
+// stored into the cache by this launch.
+ARLE_API int arle_paged_attention_decode_stream_prep(const void* q, int q_row_stride, void* out, const void* k_cache,
+                                                     const void* v_cache, long long cache_pages, const int* q_indptr,
+                                                     const int* kv_lens, const int* block_table, int bt_stride, int bt_width,
+                                                     float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
+                                                     int page_size, float scale, int window, int rows, int ctas, int fused,
+                                                     const int* slot_mapping, const float* q_weight, const float* k_weight,
+                                                     float eps, const float* inv_freq, int* err, cudaStream_t s) {
   if (rows <= 0) return 0;
+  if (fused && (!slot_mapping || ((uintptr_t)q & 15) || (q_row_stride % 8) != 0)) return ARLE_E_BADARG;
+  const Prep prep{fused ? 1 : 0, slot_mapping, q_weight, k_weight, eps, inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || page_size <= 0 || page_size % 16 != 0) return ARLE_E_UNSUPPORTED;
   if (ctas < 1 || ctas > 1024 || rows > 2048 || !part_o || !part_ml || !counters) return ARLE_E_BADARG;
   if ((q_row_stride % 2) != 0 || ((uintptr_t)q & 3) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return ARLE_E_UNSUPPORTED;
@@ -569,7 +687,7 @@ ARLE_API int arle_paged_attention_decode_stream(const void* q, int q_row_stride,
   if (rc) return rc;
   if (hd == 128)
     return launch_stream<128>(mk, mv, q, q_row_stride, out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                              rows, nq, nkv, bt_width, page_size, scale, window, ctas, err, s);
+                              rows, nq, nkv, bt_width, page_size, scale, window, ctas, prep, err, s);
   return launch_stream<64>(mk, mv, q, q_row_stride, out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                           rows, nq, nkv, bt_width, page_size, scale, window, ctas, err, s);
+                           rows, nq, nkv, bt_width, page_size, scale, window, ctas, prep, err, s);
 }

@@ -48,6 +48,8 @@ _SIGNATURES = {
     "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
                                            _F, _I, _I, _I, _P, _P],
+    "arle_paged_attention_decode_stream_prep": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
+                                                _F, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P],
     "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                                         _I, _I, _I, _P, _P],
@@ -562,6 +564,50 @@ def paged_attention_decode_stream(q, out, k_cache, v_cache, q_indptr, kv_lens, b
         _ptr(block_table), block_table.stride(0), block_table.shape[1], _ptr(piece_o), _ptr(piece_ml), _ptr(counters),
         nq, nkv, hd, page_size, float(scale), int(window) if window else 0, R, int(ctas), _ptr(error_flag(q.device)),
         _stream()), "paged_attention_decode_stream")
+
+
+def fused_decode_supported(qkv, batch, cache_dtype, nq: int, nkv: int, hd: int, page_size: int, rotary_dim: int) -> bool:
+    """Whether a step's attention can run as ONE launch that also prepares the queries and the new keys
+    (``decode_attention_with_prep``): every row of the step one decoded token, bfloat16, the shapes the
+    streaming kernel takes, and a rotation of the whole head or none."""
+    return (_KERNEL_SET == "fast" and batch is not None and batch.max_q_len == 1 and qkv.is_cuda
+            and qkv.dtype == torch.bfloat16 and cache_dtype == torch.bfloat16 and hd in (64, 128) and nq % nkv == 0
+            and nq // nkv <= 16 and rotary_dim in (0, hd) and stream_decode_supported(batch.num_rows, page_size, nq // nkv)
+            and qkv.stride(1) == 1 and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)
+
+
+def decode_attention_with_prep(qkv, out, k_cache, v_cache, slot_mapping, q_weight, k_weight, eps: float, inv_freq,
+                               block_table, nq: int, nkv: int, hd: int, page_size: int, scale: float, window, batch) -> None:
+    """Attention of a step in which every row is one decoded token, from the raw projection output
+    qkv [T, (nq + 2 nkv) hd]: per-head norm and rotation of the queries and of the new keys, the store of
+    the new keys and values into the cache, and the attention over the cache, in one launch of the
+    streaming kernel.  ``q_weight`` / ``k_weight`` None: no norm; ``inv_freq`` None: no rotation."""
+    T = qkv.shape[0]
+    if not fused_decode_supported(qkv, batch, k_cache.dtype, nq, nkv, hd, page_size, hd if inv_freq is not None else 0):
+        raise KernelError("decode_attention_with_prep: this step or these shapes need the separate preparation kernel")
+    if out.shape != (T, nq * hd) or not out.is_contiguous() or out.dtype != torch.bfloat16 or qkv.shape[1] < (nq + 2 * nkv) * hd:
+        raise KernelError("decode_attention_with_prep: out must be contiguous bfloat16 [T, nq*hd] and qkv hold q, k and v heads")
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape or not (
+            k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise KernelError(f"decode_attention_with_prep: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
+    for w_ in (q_weight, k_weight):
+        if w_ is not None and (w_.dtype != torch.float32 or w_.numel() != hd):
+            raise KernelError("decode_attention_with_prep: norm weights must be float32 [head_dim]")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.numel() != hd // 2):
+        raise KernelError("decode_attention_with_prep: inv_freq must be float32 [head_dim / 2]")
+    _i32(slot_mapping, "slot_mapping"), _i32(block_table, "block_table")
+    R, G = batch.num_rows, nq // nkv
+    ctas = sm_count(qkv.device)
+    slots = (ctas + R * nkv) * G
+    piece_o = batch.ws.get("attn_piece_o", (slots * hd,), torch.float32)
+    piece_ml = batch.ws.get("attn_piece_ml", (slots * 2,), torch.float32)
+    counters = batch.ws.get_zeroed("attn_piece_counters", (R * nkv,), torch.int32)
+    _check(library().arle_paged_attention_decode_stream_prep(
+        _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(batch.q_indptr),
+        _ptr(batch.kv_lens), _ptr(block_table), block_table.stride(0), block_table.shape[1], _ptr(piece_o), _ptr(piece_ml),
+        _ptr(counters), nq, nkv, hd, page_size, float(scale), int(window) if window else 0, R, int(ctas), 1,
+        _ptr(slot_mapping), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), _ptr(error_flag(qkv.device)),
+        _stream()), "decode_attention_with_prep")
 
 
 def decode_splits(rows: int, nkv: int, kv_bound: int, device=None) -> int:

@@ -96,9 +96,17 @@ class Attention(Mixer):
         rot = self.position.rotary() if self.position is not None else None
         inv_freq, rdim = rot if rot is not None else (None, 0)
         eps = s.qk_norm_eps if s.qk_norm_eps is not None else 0.0
+        attn = ctx.ws.get("attn_out", (T, nq * hd), x.dtype)
         if cache.writable:
             qkv = ctx.ws.get("qkv", (T, (nq + 2 * nkv) * hd), x.dtype)
             ops.gemm(x, self.w_qkv, qkv)
+            if ops.fused_decode_supported(qkv, ctx, cache.k.dtype, nq, nkv, hd, cache.page_size, rdim):
+                # a step of decoded tokens only: norm, rotation, cache store and attention in one launch
+                ops.decode_attention_with_prep(qkv, attn, cache.k, cache.v, cache.slot_mapping, self.q_norm, self.k_norm, eps,
+                                               inv_freq if rdim else None, cache.block_table, nq, nkv, hd, cache.page_size,
+                                               s.scale, s.window, ctx)
+                out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)
+                return None if ops.gemm(attn, self.w_o, out, sink=sink) else out
             ops.attention_prep(qkv, ctx.positions, cache.slot_mapping, self.q_norm, self.k_norm, eps, inv_freq, rdim,
                                cache.k, cache.v, nq, nkv, hd, cache.page_size)
         else:
@@ -106,7 +114,6 @@ class Attention(Mixer):
             ops.gemm(x, self.w_qkv[: nq * hd], qkv)
             ops.attention_prep(qkv, ctx.positions, None, self.q_norm, None, eps, inv_freq, rdim, None, None, nq, 0, hd,
                                cache.page_size)
-        attn = ctx.ws.get("attn_out", (T, nq * hd), x.dtype)
         ops.paged_attention(qkv[:, : nq * hd], attn, cache.k, cache.v, ctx.positions, ctx.row_of_token,
                             cache.block_table, nq, nkv, hd, cache.page_size, s.scale, s.window, batch=ctx)
         out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)

@@ -482,6 +482,47 @@ def test_decode_attention_stream_kernel(nq, nkv, hd, ps, window, ctas):
         assert scratch[2].abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("norm,rot", [(True, True), (False, True), (True, False)])
+@pytest.mark.parametrize("nq,nkv,hd,ps,window,lens", [
+    (32, 8, 128, 16, None, [2049] * 8), (32, 8, 128, 16, None, [1, 63, 64, 65, 700, 2049, 17, 128]),
+    (6, 1, 64, 16, None, [5, 300, 1024]), (16, 1, 128, 32, None, [2000]), (4, 4, 128, 16, 100, [1, 99, 100, 101, 640]),
+    (8, 2, 64, 48, 33, [97, 48, 49, 1]), (2, 1, 128, 64, None, [64 * k + d for k in (1, 3) for d in (-1, 0, 1)]),
+    (8, 8, 64, 16, None, [int(x) for x in torch.randint(1, 500, (70,), generator=torch.Generator().manual_seed(5))])])
+def test_decode_attention_with_fused_preparation(nq, nkv, hd, ps, window, lens, norm, rot):
+    """One launch that norms and rotates the queries and the new keys, stores the new keys and values and
+    attends, against the preparation kernel followed by the attention kernel: the same arithmetic in the
+    same order, so the same bits in the output and in the cache (also at the first token of a sequence, at
+    the edges of tiles and pages, and with pieces of several rows in one CTA)."""
+    from types import SimpleNamespace
+    from arle_b200.engine import Workspace
+
+    R, eps = len(lens), 1e-5
+    _, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, [1] * R, seed=3)
+    qkv = rnd(R, (nq + 2 * nkv) * hd + 8, dtype=torch.bfloat16, seed=7)[:, : (nq + 2 * nkv) * hd]     # rows with a stride of their own
+    qw = (1 + 0.2 * rnd(hd, seed=8)).contiguous() if norm else None
+    kw = (1 + 0.2 * rnd(hd, seed=9)).contiguous() if norm else None
+    inv_freq = torch.pow(torch.tensor(1e4), -torch.arange(hd // 2, dtype=torch.float32) * 2 / hd).to(DEV) if rot else None
+    last = kv.long() - 1
+    slots = (bt[torch.arange(R, device=DEV), last // ps].long() * ps + last % ps).to(torch.int32)
+    assert torch.equal(pos.long(), last)
+    # the two-kernel way
+    qkv_a, kc_a, vc_a = qkv.clone(), kc.clone(), vc.clone()
+    ops.attention_prep(qkv_a, pos, slots, qw, kw, eps, inv_freq, hd if rot else 0, kc_a, vc_a, nq, nkv, hd, ps)
+    want = torch.zeros(R, nq * hd, dtype=torch.bfloat16, device=DEV)
+    _stream_decode(qkv_a[:, : nq * hd], want, kc_a, vc_a, qi, kv, bt, nq, nkv, hd, ps, window, ops.sm_count(DEV))
+    # the one-kernel way
+    kc_b, vc_b = kc.clone(), vc.clone()
+    batch = SimpleNamespace(max_q_len=1, num_rows=R, ws=Workspace(DEV), q_indptr=qi, kv_lens=kv)
+    assert ops.fused_decode_supported(qkv, batch, kc.dtype, nq, nkv, hd, ps, hd if rot else 0)
+    got = torch.full((R, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    for _ in range(2):
+        ops.decode_attention_with_prep(qkv, got, kc_b, vc_b, slots, qw, kw, eps, inv_freq, bt, nq, nkv, hd, ps,
+                                       1 / math.sqrt(hd), window, batch)
+        ops.check_errors(DEV)
+        assert torch.equal(kc_b, kc_a) and torch.equal(vc_b, vc_a)
+        assert torch.equal(got, want)
+
+
 @pytest.mark.parametrize("ctas", [7, 148])
 def test_decode_attention_stream_many_rows(ctas):
     """More rows than one warp scans at once, lengths of every kind, prompt rows in between."""
