@@ -113,6 +113,7 @@ def main() -> int:
     ap.add_argument("--pdl", type=int, nargs="?", const=1, default=0,
                     help="programmatic dependent launch: 1 every kernel, 2 the weight-streaming products only")
     ap.add_argument("--tcgen05-gemm", action="store_true", help="products of 128 rows and more through the package's tcgen05 kernel instead of cuBLAS")
+    ap.add_argument("--gated-min-rows", type=int, default=None, help="rows from which the gated product runs on the two-SM tcgen05 kernel (default: the package's)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -141,6 +142,8 @@ def main() -> int:
         ops.set_programmatic_launch(args.pdl)
     if args.tcgen05_gemm:
         ops.set_tcgen05_min_rows(128)
+    if args.gated_min_rows is not None:
+        ops.set_gated_tcgen05_min_rows(args.gated_min_rows)
     pk = peaks()
     sizes = SIZES[args.sizes]
     layers = args.layers or sizes["num_hidden_layers"]

@@ -257,6 +257,35 @@ def test_gemm_tcgen05(M, N, K, out_dtype):
     assert err <= (3e-5 if out_dtype == torch.float32 else 6e-3) * max(scale, 1.0), (err, scale)
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (257, 512, 128), (300, 1000, 328), (2048, 4096, 4096), (511, 6144, 1024),
+                                   (1024, 768, 12288), (129, 260, 72), (5000, 520, 256)])
+def test_gemm_tcgen05_pair(M, N, K, out_dtype):
+    """Two SMs to a 256 x 256 tile: rows and columns that fill no tile, a K that fills no block, few and many tiles."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=2)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_tcgen05_pair(x, w, out)
+    ops.check_errors(DEV)
+    exp = x.double() @ w.double().t()
+    err = (out.double() - exp).abs().max().item()
+    assert err <= (2e-5 if out_dtype == torch.float32 else 6e-3) * max(exp.abs().max().item(), 1.0), err
+    again = torch.empty_like(out)
+    ops.gemm_tcgen05_pair(x, w, again)
+    assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize("M,I,K", [(256, 128, 64), (300, 500, 192), (2048, 12288, 4096), (777, 1536, 1024)])
+def test_gemm_tcgen05_pair_gated(M, I, K):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(2 * I, K, dtype=torch.bfloat16, scale=0.08, seed=2)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tcgen05_pair(x, w, out, gated=True)
+    ops.check_errors(DEV)
+    g, u = x.double() @ w[0::2].double().t(), x.double() @ w[1::2].double().t()
+    exp = g / (1 + torch.exp(-g)) * u
+    assert (out.double() - exp).abs().max().item() <= 1.5e-2 * max(exp.abs().max().item(), 1.0)
+
+
 def _paged_setup(dtype, nq, nkv, hd, ps, lens, q_lens, seed=0):
     """Random cache contents for requests of the given lengths, scattered pages."""
     g = torch.Generator().manual_seed(seed)
