@@ -95,6 +95,53 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+def gemm_table(args, sizes, torch, ops) -> int:
+    """The four projections of a layer at --prefill-tokens rows: cuBLAS (torch.mm) against the package's one-SM
+    and two-SM tcgen05 kernels, CUDA events over --steps back-to-back launches on rotating weights (more
+    than L2 holds).  One JSON line."""
+    dev, rows = "cuda:0", args.prefill_tokens
+    H, I = sizes["hidden_size"], sizes["intermediate_size"]
+    dq = sizes["num_attention_heads"] * sizes["head_dim"]
+    dkv = sizes["num_key_value_heads"] * sizes["head_dim"]
+    shapes = {"qkv": (dq + 2 * dkv, H), "o": (H, dq), "gate_up": (2 * I, H), "down": (H, I)}
+    steps = max(3, min(args.steps, 40))
+
+    def timed(fn):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return round(e0.elapsed_time(e1) / steps * 1000.0, 1)
+
+    table = {}
+    for name, (N, K) in shapes.items():
+        if args.gemm_product not in ("all", name):
+            continue
+        copies = max(2, int(300e6 // (N * K * 2)) + 1)
+        ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        xs = [torch.randn(rows, K, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+        out = torch.empty(rows, N, device=dev, dtype=torch.bfloat16)
+        row = {"N": N, "K": K,
+               "cublas_us": timed(lambda i: torch.mm(xs[i % 4], ws[i % copies].t(), out=out)),
+               "one_sm_us": timed(lambda i: ops.gemm_tcgen05(xs[i % 4], ws[i % copies], out)),
+               "two_sm_us": timed(lambda i: ops.gemm_tcgen05_pair(xs[i % 4], ws[i % copies], out))}
+        if name == "gate_up":
+            act = torch.empty(rows, N // 2, device=dev, dtype=torch.bfloat16)
+            row["gate_kernel_us"] = timed(lambda i: ops.silu_mul(out, act))
+            row["two_sm_gated_us"] = timed(lambda i: ops.gemm_tcgen05_pair(xs[i % 4], ws[i % copies], act, gated=True))
+        row["tflops_two_sm"] = round(2.0 * rows * N * K / row["two_sm_us"] / 1e6, 1)
+        table[name] = row
+        del ws, xs, out
+    ops.check_errors(dev)
+    print(json.dumps({"only": "gemm", "rows": rows, "steps": steps, "products": table}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -105,8 +152,11 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--sizes", choices=sorted(SIZES), default="8b", help="layer sizes (default: Qwen3-8B, the contract's)")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
-                    help="profiling aid: run only the decode steps at --batch, or only the prefill")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm"],
+                    help="profiling aid: run only the decode steps at --batch, only the prefill, or (gemm) the four "
+                         "projections of a layer at --prefill-tokens rows on cuBLAS and on the package's tcgen05 kernels")
+    ap.add_argument("--gemm-product", default="all", choices=["all", "qkv", "o", "gate_up", "down"],
+                    help="with --only gemm: one product only (for a profiler capture)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: tokens each request holds")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: tokens of the prompt")
     ap.add_argument("--no-cuda-graph", action="store_true")
@@ -146,6 +196,8 @@ def main() -> int:
         ops.set_gated_tcgen05_min_rows(args.gated_min_rows)
     pk = peaks()
     sizes = SIZES[args.sizes]
+    if args.only == "gemm":
+        return gemm_table(args, sizes, torch, ops)
     layers = args.layers or sizes["num_hidden_layers"]
     model = random_model(sizes, seed=0, dtype="bfloat16", device=dev, num_layers=layers)
     spec = model.spec
