@@ -151,6 +151,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than Qwen3-8B's 36 (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--more-points", action="store_true",
+                    help="also decode at Qwen3-0.6B and Qwen3-32B layer sizes and at 8,192 / 32,768-token contexts (points_more)")
     ap.add_argument("--sizes", choices=sorted(SIZES), default="8b", help="layer sizes (default: Qwen3-8B, the contract's)")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "gemm"],
                     help="profiling aid: run only the decode steps at --batch, only the prefill, or (gemm) the four "
@@ -205,23 +207,30 @@ def main() -> int:
     page = 16
     max_batch = max(64, args.batch) if args.only == "all" else (args.batch if args.only == "decode" else 1)
     per_req = max(CONTEXT + args.steps + args.warmup + 64, PREFILL_TOKENS + 64 if args.only != "decode" else 0)
-    pages = max_batch * -(-per_req // page) + 64
-    runner = ModelRunner(model, page, pages, max_batch, max(CONTEXT * 2 + 1024, per_req), dev)
-    if not args.no_cuda_graph:
-        runner.enable_graphs()
-    for g in runner.cache.groups:
-        for a in g.arrays:
-            a.normal_(0.0, 0.5)                                  # synthetic cache contents
-    sampler = Sampler(vocab, dev)
+    def make_runner(model, max_batch, per_req):
+        pages = max_batch * -(-per_req // page) + 64
+        r = ModelRunner(model, page, pages, max_batch, per_req + 1024, dev)
+        if not args.no_cuda_graph:
+            r.enable_graphs()
+        for g in r.cache.groups:
+            for a in g.arrays:
+                a.normal_(0.0, 0.5)                              # synthetic cache contents
+        return r
+
+    runner = main_runner = make_runner(model, max_batch, per_req)
+    sampler = main_sampler = Sampler(vocab, dev)
     gen = torch.Generator().manual_seed(1)
     weight_bytes = model.weight_bytes_per_step()
     kv_bytes_per_token = runner.cache.bytes_per_token()
 
-    def decode_run(batch, steps, warmup, clocks=None):
+    def decode_run(batch, steps, warmup, clocks=None, runner=None, sampler=None, context=None, stats=None):
+        runner = runner or main_runner
+        sampler = sampler or main_sampler
+        context = context or CONTEXT
         rids = [f"b{batch}-{i}" for i in range(batch)]
         for r in rids:
             runner.add_request(r)
-        runner.cache.append([(r, CONTEXT - 1) for r in rids])      # contexts of 2,047 tokens; the first step makes 2,048
+        runner.cache.append([(r, context - 1) for r in rids])      # contexts of context - 1 tokens; the first step completes them
         toks = torch.randint(0, vocab, (batch,), generator=gen).tolist()
         greedy = [SamplingParams()] * batch
         first = runner.step([StepEntry(r, [t], (0,)) for r, t in zip(rids, toks)])
@@ -240,16 +249,19 @@ def main() -> int:
         if clocks:
             clocks.start()
         l0 = ops.launch_count()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        marks[0].record()
+        for i in range(steps):
             one()
-        e1.record()
+            marks[i + 1].record()
         torch.cuda.synchronize()
         pending.pop(0).result()
-        ms = e0.elapsed_time(e1) / steps
+        ms = marks[0].elapsed_time(marks[-1]) / steps           # the K steps as one interval: the contract's figure
+        per_step = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+        if stats is not None:
+            stats["median_ms"] = per_step[steps // 2]
         launches = ops.launch_count() - l0
-        ctx_mid = CONTEXT + 1 + warmup + steps // 2
+        ctx_mid = context + 1 + warmup + steps // 2
         for r in rids:
             runner.end_request(r)
         return ms, launches, ctx_mid
@@ -260,7 +272,9 @@ def main() -> int:
                           "gpu_launches": int(launches)}))
         return 0
     clocks = ClockSampler()
-    ms, launches, ctx_mid = (0.0, 0, CONTEXT) if args.only == "prefill" else decode_run(args.batch, args.steps, args.warmup, clocks)
+    stats = {}
+    ms, launches, ctx_mid = (0.0, 0, CONTEXT) if args.only == "prefill" else decode_run(args.batch, args.steps, args.warmup, clocks,
+                                                                                        stats=stats)
     clk = clocks.stop()
     value = args.batch * 1000.0 / ms if ms else 0.0
     step_bytes = weight_bytes + args.batch * ctx_mid * kv_bytes_per_token
@@ -306,6 +320,7 @@ def main() -> int:
     e2e = None
     if not args.no_e2e:
         del runner
+        main_runner = None
         torch.cuda.empty_cache()
         n_new = args.steps + 1
         eng = Engine(model=model, options=EngineOptions(
@@ -330,10 +345,42 @@ def main() -> int:
         e2e = {"value": round(decoded / dt, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(eng.runner.last_ctx.h2d_bytes),
                "d2h_bytes_per_step": 4 * args.batch, "decoded_tokens": decoded}
 
+    # further sizes and contexts, off by default: Qwen3-0.6B and Qwen3-32B layer sizes at their own contexts, and
+    # the 8B sizes at longer contexts; tokens per second, device-timed like ``points``
+    more = {}
+    if args.more_points:
+        import gc
+        steps_m = max(8, args.steps // 4)
+        if "eng" in locals():
+            del eng
+        main_runner = runner = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        for ctx_len in (8192, 32768):
+            r = make_runner(model, 8, ctx_len + steps_m + args.warmup + 64)
+            m, _, _ = decode_run(8, steps_m, args.warmup, runner=r, sampler=main_sampler, context=ctx_len)
+            more[f"8b_decode_b8_ctx{ctx_len}"] = round(8 * 1000.0 / m, 1)
+            del r
+            gc.collect()
+            torch.cuda.empty_cache()
+        del model
+        gc.collect()
+        torch.cuda.empty_cache()
+        for name, ctx_len in (("0.6b", 1152), ("32b", 2048)):
+            mdl = random_model(SIZES[name], seed=0, dtype="bfloat16", device=dev)
+            r = make_runner(mdl, 64, ctx_len + steps_m + args.warmup + 64)
+            smp = Sampler(mdl.spec.vocab_size, dev)
+            for b in (1, 8, 64):
+                m, _, _ = decode_run(b, steps_m, args.warmup, runner=r, sampler=smp, context=ctx_len)
+                more[f"{name}_decode_b{b}_ctx{ctx_len}"] = round(b * 1000.0 / m, 1)
+            del r, smp, mdl
+            gc.collect()
+            torch.cuda.empty_cache()
+
     out = {
         "metric": f"decode tokens/s at batch {args.batch}, 2048-token context (Qwen3-{args.sizes.upper()} sizes, bf16, one B200)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(ms, 4), "ms_per_step_median": round(stats.get("median_ms", ms), 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded random weights, uniform random token ids, random cache contents)",
         "impl": "ours",
         "config": {"model": f"Qwen3-{args.sizes.upper()} sizes, random weights", "layers": layers,
@@ -349,6 +396,7 @@ def main() -> int:
                      "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"], "bytes_per_step": int(step_bytes)},
         "points": points,
         "e2e": e2e,
+        **({"points_more": more} if more else {}),
         "gpu_launches": int(launches),
         "clocks": clk,
     }
