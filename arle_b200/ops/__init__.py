@@ -176,7 +176,9 @@ def _ptr(t, name="tensor"):
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    # torch's raw-stream query: a plain C call (torch.cuda.current_stream() builds a Python object and costs
+    # some 15 us, once per launch)
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def _check(code: int, what: str):
