@@ -191,6 +191,13 @@ class DecayMixer(Mixer):
     def forward(self, x, ctx, cache, state):
         assert cache is None
         u = x.float() @ self.w_in.t()
+        if ctx.max_q_len == 1:
+            # one token a row: no loop over rows and nothing read back to the host, so that the step can be
+            # captured in a CUDA graph
+            slots = ctx.state_slots.long()
+            s = self.spec.decay * state[slots] + u
+            state.index_copy_(0, slots, s)
+            return (s @ self.w_out.t()).to(x.dtype)
         out = torch.empty_like(u)
         at = 0
         for r, n in enumerate(ctx.q_lens):
@@ -246,3 +253,18 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     runner.end_request("a")
     got_c = runner.step([StepEntry("c", a, range(len(a)))]).clone()       # takes a's slot: the state starts at zero again
     assert (got_c.double().cpu() - plain_toy(a)).abs().max() < 1e-4
+    runner.end_request("b")
+    runner.end_request("c")
+    # decode steps as CUDA graphs: the step in which a graph is captured must advance the state once, not twice
+    runner.enable_graphs()
+    seqs = {"d": [int(t) for t in torch.randint(0, V, (30,), generator=torch.Generator().manual_seed(1))],
+            "e": [int(t) for t in torch.randint(0, V, (26,), generator=torch.Generator().manual_seed(2))]}
+    got = {r: [runner.step([StepEntry(r, t[:6], range(6))]).clone()] for r, t in seqs.items()}
+    for i in range(6, 30):
+        rows = [r for r, t in seqs.items() if i < len(t)]
+        lg = runner.step([StepEntry(r, seqs[r][i:i + 1], (0,)) for r in rows]).clone()
+        for k, r in enumerate(rows):
+            got[r].append(lg[k:k + 1])
+    assert runner.graph_steps == 24 and len(runner._graphs) == 2          # graphs of two rows and of one row
+    for r, t in seqs.items():
+        assert (torch.cat(got[r]).double().cpu() - plain_toy(t)).abs().max() < 1e-4
