@@ -162,6 +162,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only decode: tokens each request holds")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: tokens of the prompt")
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --only decode: also the kernels of one graph-replayed step in order, with the device time "
+                         "of each (from torch's profiler: shares of the step, not a benchmark figure)")
     ap.add_argument("--pdl", type=int, nargs="?", const=1, default=0,
                     help="programmatic dependent launch: 1 every kernel, 2 the weight-streaming products only")
     ap.add_argument("--tcgen05-gemm", action="store_true", help="products of 128 rows and more through the package's tcgen05 kernel instead of cuBLAS")
@@ -268,8 +271,19 @@ def main() -> int:
 
     if args.only == "decode":
         ms, launches, _ = decode_run(args.batch, args.steps, args.warmup)
-        print(json.dumps({"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4),
-                          "gpu_launches": int(launches)}))
+        rec = {"only": "decode", "batch": args.batch, "layers": layers, "ms_per_step": round(ms, 4), "gpu_launches": int(launches)}
+        if args.timeline:
+            from torch.profiler import ProfilerActivity, profile
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                decode_run(args.batch, 3, 3)
+            evs = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                          if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda t: t[0])
+            last = max(i for i, k in enumerate(evs) if "embedding" in k[2])          # the last step starts with the embedding
+            step = evs[last:]
+            rec["timeline_span_us"] = round(step[-1][1] - step[0][0], 1)
+            rec["timeline"] = [[k[2].replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0][:48],
+                                round(k[1] - k[0], 2)] for k in step]
+        print(json.dumps(rec))
         return 0
     clocks = ClockSampler()
     stats = {}
