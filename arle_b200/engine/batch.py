@@ -106,6 +106,7 @@ class StepContext:
         self.last_token: Optional[torch.Tensor] = None       # int32 [slots]: each request's last sampled token
         self.h2d_bytes = 0
         self.groups: List[GroupTables] = []
+        self.memo: dict = {}                                 # what parts derive from a step once for all layers (cleared per step)
         self._pinned: Optional[torch.Tensor] = None
         self._dev: Optional[torch.Tensor] = None
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None

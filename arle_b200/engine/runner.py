@@ -114,7 +114,7 @@ class ModelRunner:
             else:
                 ctx = self.ctx.build(entries, starts)
                 with ops.use_kernel_set(self.kernel_set):
-                    logits = self.model.forward(ctx)
+                    logits = _forward(self.model, ctx)
         except Exception:
             for e, s in zip(entries, starts):
                 self.cache.truncate(e.request, s)
@@ -125,6 +125,13 @@ class ModelRunner:
         self.tokens_run += ctx.num_tokens
         self.last_ctx = ctx
         return logits
+
+
+def _forward(model, ctx):
+    """One pass of the model over a step.  What parts keep in ``ctx.memo`` is derived by the pass that uses it:
+    a step that runs twice (eagerly, then under capture) derives it twice, so that the capture holds those launches."""
+    ctx.memo.clear()
+    return model.forward(ctx)
 
 
 class _DecodeGraph:
@@ -155,7 +162,7 @@ class _DecodeGraph:
             # the step has run exactly once and its logits stand.
             model = self.runner.model
             with ops.use_kernel_set(self.runner.kernel_set):
-                model.forward(ctx)
+                _forward(model, ctx)
                 torch.cuda.synchronize(self.runner.device)
                 # No graph may be destroyed while a stream captures (it invalidates the capture):
                 # collect what is garbage now, an earlier engine's graphs for one, and keep the
@@ -168,7 +175,7 @@ class _DecodeGraph:
                     before = ops.launch_count()
                     graph = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(graph):
-                        self.logits = model.forward(ctx)
+                        self.logits = _forward(model, ctx)
                     self.launches = ops.launch_count() - before
                 finally:
                     self.ws.frozen = False

@@ -43,7 +43,8 @@ _SIGNATURES = {
     "arle_rmsnorm": [_P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "arle_residual_add": [_P, _P, _I, _I, _I, _P],
     "arle_silu_mul": [_P, _P, _I, _I, _I, _P],
-    "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_attention_prep": [_P, _I, _I, _P, _P, _P, _P, _F, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "arle_rotary_angles": [_P, _P, _P, _I, _I, _P],
     "arle_paged_attention_plain": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "arle_paged_attention_decode": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
@@ -433,12 +434,33 @@ def skinny_gemm_supported(x, w, out) -> bool:
 
 
 # ------------------------------------------------------------------- attention
+def rotary_angles(positions, inv_freq, out) -> None:
+    """out[t, i] = (cos, sin)(positions[t] * inv_freq[i]) in float32, [T, len(inv_freq), 2]: what
+    ``attention_prep`` evaluates for every layer of a step, once."""
+    T, half = positions.numel(), inv_freq.numel()
+    if (out.dtype != torch.float32 or tuple(out.shape) != (T, half, 2) or not out.is_contiguous()
+            or inv_freq.dtype != torch.float32):
+        raise KernelError("rotary_angles: out must be contiguous float32 [T, len(inv_freq), 2]")
+    _i32(positions, "positions")
+    _check(library().arle_rotary_angles(_ptr(positions), _ptr(inv_freq), _ptr(out), T, half, _stream()), "rotary_angles")
+
+
+def attention_prep_takes_angles(qkv, hd: int, rotary_dim: int) -> bool:
+    """Whether ``attention_prep`` would use a table of ``rotary_angles`` for this input (the kernel for
+    prompt portions does; the others evaluate the angles themselves)."""
+    return qkv.dtype == torch.bfloat16 and qkv.shape[0] >= 32 and hd in (64, 128) and rotary_dim == hd
+
+
 def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, k_cache, v_cache,
-                   nq: int, nkv: int, hd: int, page_size: int) -> None:
+                   nq: int, nkv: int, hd: int, page_size: int, angles=None) -> None:
     """Per-head q/k RMSNorm (weights float32 [hd] or None), rotary encoding, and the
     store of k and v into the paged cache, in place on qkv [T, (nq + 2 nkv) hd]
-    (nkv = 0: the rows hold q only and nothing is stored)."""
+    (nkv = 0: the rows hold q only and nothing is stored).  ``angles``: the table of
+    ``rotary_angles`` for these positions and inv_freq, or None."""
     T = qkv.shape[0]
+    if angles is not None and (angles.dtype != torch.float32 or tuple(angles.shape) != (T, rotary_dim // 2, 2)
+                               or not angles.is_contiguous()):
+        raise KernelError("attention_prep: angles must be contiguous float32 [T, rotary_dim / 2, 2]")
     if qkv.stride(1) != 1 or qkv.shape[1] < (nq + 2 * nkv) * hd:
         raise KernelError("attention_prep: qkv must be [T, >= (nq + 2 nkv) hd] with unit inner stride")
     if hd % 2 or hd > 256:
@@ -459,7 +481,8 @@ def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_fr
         raise KernelError("attention_prep: inv_freq must be float32 [rotary_dim / 2]")
     _check(library().arle_attention_prep(
         _ptr(qkv), _dt(qkv), qkv.stride(0), _ptr(positions), _ptr(slot_mapping), _ptr(q_weight), _ptr(k_weight),
-        float(eps), _ptr(inv_freq) if rotary_dim else None, int(rotary_dim), _ptr(k_cache) if nkv else None,
+        float(eps), _ptr(inv_freq) if rotary_dim else None, _ptr(angles) if rotary_dim else None, int(rotary_dim),
+        _ptr(k_cache) if nkv else None,
         _ptr(v_cache) if nkv else None, nq, nkv, hd, page_size, T, _stream()), "attention_prep")
 
 

@@ -88,6 +88,19 @@ class Attention(Mixer):
     def can_sink(self, num_rows):
         return ops.fused_gemm_shape_ok(num_rows, self.w_o)
 
+    def _angles(self, qkv, ctx, inv_freq, rdim):
+        """Cosines and sines of the step's positions, evaluated once for all layers that rotate by the same
+        frequencies (kept in the step's memo under the encoding's description)."""
+        if not rdim or not ops.attention_prep_takes_angles(qkv, self.spec.head_dim, rdim):
+            return None
+        key = ("rotary_angles", getattr(self.position, "spec", None) or id(self.position))
+        angles = ctx.memo.get(key)
+        if angles is None:
+            angles = ctx.ws.get(f"rotary_angles_{len(ctx.memo)}", (qkv.shape[0], rdim // 2, 2), torch.float32)
+            ops.rotary_angles(ctx.positions, inv_freq, angles)
+            ctx.memo[key] = angles
+        return angles
+
     # ---------------------------------------------------------------- forward
     def forward(self, x, ctx, cache, state, sink=None):
         s = self.spec
@@ -108,12 +121,12 @@ class Attention(Mixer):
                 out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)
                 return None if ops.gemm(attn, self.w_o, out, sink=sink) else out
             ops.attention_prep(qkv, ctx.positions, cache.slot_mapping, self.q_norm, self.k_norm, eps, inv_freq, rdim,
-                               cache.k, cache.v, nq, nkv, hd, cache.page_size)
+                               cache.k, cache.v, nq, nkv, hd, cache.page_size, angles=self._angles(qkv, ctx, inv_freq, rdim))
         else:
             qkv = ctx.ws.get("q_only", (T, nq * hd), x.dtype)
             ops.gemm(x, self.w_qkv[: nq * hd], qkv)
             ops.attention_prep(qkv, ctx.positions, None, self.q_norm, None, eps, inv_freq, rdim, None, None, nq, 0, hd,
-                               cache.page_size)
+                               cache.page_size, angles=self._angles(qkv, ctx, inv_freq, rdim))
         ops.paged_attention(qkv[:, : nq * hd], attn, cache.k, cache.v, ctx.positions, ctx.row_of_token,
                             cache.block_table, nq, nkv, hd, cache.page_size, s.scale, s.window, batch=ctx)
         out = ctx.ws.get("mixer_out", (T, s.hidden_size), x.dtype)

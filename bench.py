@@ -315,7 +315,17 @@ def main() -> int:
         prefill_once(f"w{i}")
     pf_ms = sorted(prefill_once(f"t{i}") for i in range(1 if args.only == "prefill" else 5))[0 if args.only == "prefill" else 2]
     if args.only == "prefill":
-        print(json.dumps({"only": "prefill", "layers": layers, "ms": round(pf_ms, 3)}))
+        rec = {"only": "prefill", "layers": layers, "ms": round(pf_ms, 3)}
+        if args.timeline:
+            from torch.profiler import ProfilerActivity, profile
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                prefill_once("prof")
+            evs = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                          if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda t: t[0])
+            rec["timeline_span_us"] = round(evs[-1][1] - evs[0][0], 1)
+            rec["timeline"] = [[k[2].replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0][:48],
+                                round(k[1] - k[0], 2)] for k in evs]
+        print(json.dumps(rec))
         return 0
     c = model.config
     mm_params = layers * (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim

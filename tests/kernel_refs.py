@@ -53,8 +53,12 @@ def fused_decode_supported(*args, **kwargs):
     return False
 
 
+def attention_prep_takes_angles(*args, **kwargs):
+    return False
+
+
 def attention_prep(qkv, positions, slot_mapping, q_weight, k_weight, eps, inv_freq, rotary_dim, k_cache, v_cache,
-                   nq, nkv, hd, page_size):
+                   nq, nkv, hd, page_size, angles=None):
     T = qkv.shape[0]
     heads = qkv[:, : (nq + 2 * nkv) * hd].view(T, nq + 2 * nkv, hd)
 
@@ -152,4 +156,4 @@ def sample(logits, temperature, top_k, top_p, min_p, uniform, scratch, out):
         out[r] = int(hit[0]) if hit.numel() else int(torch.nonzero(p > 0)[-1])
 
 
-ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "fused_decode_supported", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample")
+ALL = ("embedding", "rmsnorm", "residual_add", "gemm", "fused_gemm_shape_ok", "fused_decode_supported", "attention_prep_takes_angles", "attention_prep", "paged_attention", "silu_mul", "gemm_silu_mul", "argmax", "scatter_tokens", "sample")

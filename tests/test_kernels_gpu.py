@@ -366,6 +366,50 @@ def test_attention_prep(dtype, nq, nkv, hd, ps, rot, norm, T):
     assert torch.equal(vc, vc2)
 
 
+@pytest.mark.parametrize("nq,nkv,hd", [(32, 8, 128), (56, 8, 128), (5, 1, 128), (5, 1, 64), (9, 3, 64), (120, 12, 64)])
+@pytest.mark.parametrize("norm", [True, False, "q"])
+def test_attention_prep_token_kernel(nq, nkv, hd, norm):
+    """The kernel for prompt portions (a block per token, 16-byte lanes, several heads to a warp at once): more heads
+    than the block takes in one round, head counts that leave lanes of a warp without a head, both head sizes."""
+    T, ps = 70, 16
+    pages = -(-T // ps) + 6
+    qkv = rnd(T, (nq + 2 * nkv) * hd, dtype=torch.bfloat16, scale=2.0, seed=1)
+    pos = torch.randint(0, 40000, (T,), dtype=torch.int32, device=DEV)
+    slots = torch.randperm(pages * ps)[:T].to(torch.int32).to(DEV)
+    slots[3] = -1
+    qw = (1.0 + 0.2 * rnd(hd, seed=2)) if norm else None
+    kw = (1.0 + 0.2 * rnd(hd, seed=3)) if norm is True else None          # "q": a query head and a key head of one warp differ
+    inv = torch.pow(torch.tensor(1e6), -2.0 * torch.arange(hd // 2) / hd).float().to(DEV)
+    kc = torch.zeros(pages, nkv, ps, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    a, b = qkv.clone(), qkv.clone()
+    kc2, vc2 = kc.clone(), vc.clone()
+    ops.attention_prep(a, pos, slots, qw, kw, 1e-6, inv, hd, kc, vc, nq, nkv, hd, ps)
+    ref.attention_prep(b, pos, slots, qw, kw, 1e-6, inv, hd, kc2, vc2, nq, nkv, hd, ps)
+    torch.testing.assert_close(a[:, :nq * hd].float(), b[:, :nq * hd].float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(kc.float(), kc2.float(), rtol=2e-2, atol=2e-2)
+    assert torch.equal(vc, vc2)
+    assert torch.equal(a[:, nq * hd:], qkv[:, nq * hd:])            # keys and values of the projection output stay
+    # the kernel for a few tokens (a warp per token and head), 16 tokens at a call: the same bits, so a key has the
+    # same bits whether its token came in a prompt portion or alone
+    d = qkv.clone()
+    kc4, vc4 = torch.zeros_like(kc), torch.zeros_like(vc)
+    for lo in range(0, T, 16):
+        ops.attention_prep(d[lo:lo + 16], pos[lo:lo + 16], slots[lo:lo + 16], qw, kw, 1e-6, inv, hd, kc4, vc4, nq, nkv, hd, ps)
+    assert torch.equal(d, a) and torch.equal(kc4, kc) and torch.equal(vc4, vc)
+    # with the step's table of cosines and sines: the same bits as with the angles evaluated in the kernel
+    assert ops.attention_prep_takes_angles(qkv, hd, hd)
+    angles = torch.empty(T, hd // 2, 2, device=DEV)
+    ops.rotary_angles(pos, inv, angles)
+    got = angles.double()
+    assert (got[..., 0] - torch.cos((pos.float()[:, None] * inv[None, :]).double())).abs().max() < 1e-6
+    assert (got[..., 1] - torch.sin((pos.float()[:, None] * inv[None, :]).double())).abs().max() < 1e-6
+    c = qkv.clone()
+    kc3, vc3 = torch.zeros_like(kc), torch.zeros_like(vc)
+    ops.attention_prep(c, pos, slots, qw, kw, 1e-6, inv, hd, kc3, vc3, nq, nkv, hd, ps, angles=angles)
+    assert torch.equal(c, a) and torch.equal(kc3, kc) and torch.equal(vc3, vc)
+
+
 def test_attention_prep_q_only():
     nq, hd, T = 4, 32, 6
     q = rnd(T, nq * hd, seed=1)
