@@ -107,9 +107,17 @@ __device__ __forceinline__ void reg_more() { asm volatile("setmaxnreg.inc.sync.a
 template <int N>
 __device__ __forceinline__ void reg_less() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(N)); }
 
-// The next block of the running launch (one launch at a time: the launches of a stream follow one another).  Every CTA
-// draws tickets until it draws one beyond the last block; the last ticket of all sets the counter back to zero.
+// The blocks of the running launch that were drawn after every CTA's first (which is the block of its own index) (one
+// launch at a time: the launches of a stream follow one another).  Every CTA draws tickets until it draws one beyond the
+// last block; the last ticket of all sets the counter back to zero.
 __device__ unsigned int g_ticket;
+
+// Ticket number gridDim.x + (draws before this one); the draw that must be the last of the launch resets the counter.
+__device__ __forceinline__ unsigned int draw_ticket(int nblocks) {
+  const unsigned int raw = atomicAdd(&g_ticket, 1u);
+  if (raw + 1 == (unsigned int)nblocks) atomicExch(&g_ticket, 0u);      // nblocks - grid blocks and grid tickets beyond them
+  return raw + gridDim.x;
+}
 
 // What a CTA's roles need to know of one block: 256 queries of one request and one query head.
 struct Block {
@@ -178,6 +186,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the CTA's first block is the one of its own index: its shape is worked out while the rest is set up
+  bool first_has_queries = false;
+  if (warp == kKeyWarp && lane == 0)
+    first_has_queries = work_blk[0].init((int)blockIdx.x, nq, nkv, nyb, q_indptr, kv_lens, window, skip_single);
   if (threadIdx.x == 0) {
     mbar_init(smem_addr(&q_full), 1);
     mbar_init(smem_addr(&q_empty), 1);
@@ -239,16 +251,17 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       for (int it = 0;; ++it) {
         if (keys && lane == 0) {
           int b = -1;
-          if (it < 2 || mbar_wait_bounded(smem_addr(&work_empty[it & 1]), (uint32_t)(((it >> 1) & 1) ^ 1), aborted)) {
+          if (it == 0) {
+            b = first_has_queries ? (int)blockIdx.x : -2;
+          } else if (it < 2 || mbar_wait_bounded(smem_addr(&work_empty[it & 1]), (uint32_t)(((it >> 1) & 1) ^ 1), aborted)) {
             if (!*aborted) {
-              const unsigned int tk = atomicAdd(&g_ticket, 1u);
-              if (tk + 1 == (unsigned int)nblocks + gridDim.x) atomicExch(&g_ticket, 0u);
+              const unsigned int tk = draw_ticket(nblocks);
               if (tk < (unsigned int)nblocks) b = (int)tk; else ended = true;
+              if (b >= 0 && !work_blk[it & 1].init(b, nq, nkv, nyb, q_indptr, kv_lens, window, skip_single)) b = -2;
             }
           } else {
             abort_flag = 1;
           }
-          if (b >= 0 && !work_blk[it & 1].init(b, nq, nkv, nyb, q_indptr, kv_lens, window, skip_single)) b = -2;
           work_id[it & 1] = b;
           asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];\n" ::"r"(smem_addr(&work_full[it & 1])) : "memory");
         }
@@ -321,11 +334,8 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       }
       if (keys && lane == 0 && !ended) {
         // a wait ran out: the tickets are still drawn to the end, so that the counter is back at zero for the next launch
-        for (int i = 0; i <= nblocks; ++i) {
-          const unsigned int tk = atomicAdd(&g_ticket, 1u);
-          if (tk + 1 == (unsigned int)nblocks + gridDim.x) atomicExch(&g_ticket, 0u);
-          if (tk >= (unsigned int)nblocks) break;
-        }
+        for (int i = 0; i <= nblocks; ++i)
+          if (draw_ticket(nblocks) >= (unsigned int)nblocks) break;
       }
       // No copy may still be in flight when the CTA ends.  The issuing thread has waited for every tile
       // unless a wait ran out, so this is free otherwise.
