@@ -197,24 +197,54 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_part_kernel(const float
   const float* x = logits + (size_t)row * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
-    const float v = x[i];
+  auto take = [&](float v, int i) {
     if (v > best || (v == best && i < bi)) { best = v; bi = i; }
-  }
-  sval[threadIdx.x] = best;
-  sidx[threadIdx.x] = bi;
-  __syncthreads();
-  for (int s = blockDim.x >> 1; s > 0; s >>= 1) {
-    if (threadIdx.x < s) {
-      const float v = sval[threadIdx.x + s];
-      const int i = sidx[threadIdx.x + s];
-      if (v > sval[threadIdx.x] || (v == sval[threadIdx.x] && i < sidx[threadIdx.x])) { sval[threadIdx.x] = v; sidx[threadIdx.x] = i; }
+  };
+  // 16-byte loads over the aligned middle of the part, four of them under way per thread; the ragged ends one by one
+  const int a0 = min(e, (int)((b + ((4 - ((reinterpret_cast<uintptr_t>(x + b) >> 2) & 3)) & 3))));
+  const int n4 = (e - a0) >> 2;
+  for (int i = b + threadIdx.x; i < a0; i += blockDim.x) take(x[i], i);
+  const float4* x4 = reinterpret_cast<const float4*>(x + a0);
+  int q = threadIdx.x;
+  for (; q + 3 * (int)blockDim.x < n4; q += 4 * blockDim.x) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = x4[q + u * blockDim.x];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = a0 + 4 * (q + u * blockDim.x);
+      take(v[u].x, i), take(v[u].y, i + 1), take(v[u].z, i + 2), take(v[u].w, i + 3);
     }
-    __syncthreads();
   }
-  if (threadIdx.x == 0) {
-    part_val[row * kArgmaxParts + part] = sval[0];
-    part_idx[row * kArgmaxParts + part] = sidx[0];
+  for (; q < n4; q += blockDim.x) {
+    const float4 v = x4[q];
+    const int i = a0 + 4 * q;
+    take(v.x, i), take(v.y, i + 1), take(v.z, i + 2), take(v.w, i + 3);
+  }
+  for (int i = a0 + 4 * n4 + threadIdx.x; i < e; i += blockDim.x) take(x[i], i);
+  // the warps' bests by shuffles, then one warp over the warps
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  if (lane == 0) sval[warp] = best, sidx[warp] = bi;
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < nwarps ? sval[lane] : -INFINITY;
+    bi = lane < nwarps ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) {
+      part_val[row * kArgmaxParts + part] = best;
+      part_idx[row * kArgmaxParts + part] = bi;
+    }
   }
 }
 

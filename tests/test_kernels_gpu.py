@@ -447,6 +447,24 @@ def test_argmax_split_kernel(R, V):
         assert out[1].item() == 0
 
 
+@pytest.mark.parametrize("V,shift", [(1003, 0), (1003, 1), (1003, 3), (4096, 2), (151936, 0)])
+def test_argmax_at_every_edge_of_its_parts(V, shift):
+    """The maximum at the first and last places of the 32 parts that the rows are cut into, in rows that start at
+    any alignment (the kernel reads 16 bytes at a time between ragged ends), and a tie across two parts."""
+    per = -(-V // 32)
+    places = sorted({p for k in range(32) for p in (k * per - 1, k * per, k * per + 1, k * per + 2, k * per + 3)
+                     if 0 <= p < V} | {V - 1, V - 2})
+    R = len(places) + 1
+    store = rnd(R, V + 8, seed=3)
+    logits = store[:, shift:shift + V]
+    for r, pl in enumerate(places):
+        logits[r, pl] = 60.0
+    logits[R - 1, per + 5] = logits[R - 1, per - 2] = logits[R - 1, 7 * per] = 70.0
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, torch.empty(R * 64, device=DEV), out)
+    assert out.tolist() == places + [per - 2]
+
+
 @pytest.mark.parametrize("V", [257, 5000])
 def test_sample_temperature_top_k_top_p(V):
     R = 8
