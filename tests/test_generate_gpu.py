@@ -264,6 +264,37 @@ def test_logits_of_graph_replayed_decode_steps(name, dtype, tmp_path):
     assert replays == len(rows_per_step)
 
 
+def test_graph_replay_of_many_rows_rebuilds_what_the_step_derives_once(tmp_path):
+    """Forty decoded rows on pages of 8 tokens (no streaming kernel for those): the step runs the preparation kernel
+    for many tokens, which takes its cosines and sines from a table that the first layer fills for all layers.  The
+    captured graph must hold the launch that fills it: a replay with the table of the captured step would rotate by
+    the wrong positions from the second step on."""
+    from arle_b200.engine import ModelRunner, StepEntry, load_model
+
+    name, R, steps = "D", 40, 6
+    d = make_model_dir(name, seed=23, root=str(tmp_path))
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    g = torch.Generator().manual_seed(5)
+    seqs = [torch.randint(0, cfg["vocab_size"], (int(n),), generator=g).tolist()
+            for n in torch.randint(steps + 2, 30, (R,), generator=g)]
+    oracle = [plain.forward(w, cfg, s) for s in seqs]
+    model = load_model(d, torch.bfloat16, "cuda")
+    runner = ModelRunner(model, 8, R * 4 + 4, R)
+    runner.enable_graphs()
+    at = [len(s) - steps for s in seqs]
+    runner.step([StepEntry(i, s[:at[i]], ()) for i, s in enumerate(seqs)])
+    before = runner.graph_steps
+    for _ in range(steps):
+        slots = torch.tensor([runner.cache.slot(i) for i in range(R)], device="cuda")
+        runner.last_token[slots] = torch.tensor([seqs[i][at[i]] for i in range(R)], dtype=torch.int32, device="cuda")
+        logits = runner.step([StepEntry(i, [-1], (0,)) for i in range(R)]).float().cpu()
+        for i in range(R):
+            err = (logits[i].double() - oracle[i][at[i]]).abs().max().item()
+            assert err <= 4e-2, f"request {i} position {at[i]}: error {err:.3g}"
+            at[i] += 1
+    assert runner.graph_steps - before == steps
+
+
 def test_command_line_run_json(models):
     d, cfg, w, prompts = models["A"]
     r = subprocess.run([sys.executable, "-m", "arle_b200", "--model-path", d, "--max-tokens", "6", "--dtype", "float32",
