@@ -118,6 +118,7 @@ class StepContext:
         the width of every block table (a captured graph needs the same layout at
         every replay); by default each is as wide as the longest request needs."""
         cm = self.cache
+        self.memo.clear()
         R = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         T = sum(q_lens)
