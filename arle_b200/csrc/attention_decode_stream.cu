@@ -165,9 +165,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(m) : "memory");
   }
   for (int r = tid; r < R; r += kThreads) {
-    const int t = q_indptr[r];
-    const bool single = q_indptr[r + 1] - t == 1;
-    const int kv_len = single ? kv_lens[r] : -1;
+    const int t = q_indptr[r], t_end = q_indptr[r + 1], len = kv_lens[r];     // three loads under way at once, not one after another
+    const bool single = t_end - t == 1;
+    const int kv_len = single ? len : -1;
     kvl[r] = kv_len;
     tok[r] = t;
     int units = 0;
