@@ -706,6 +706,31 @@ def test_prefill_attention_tcgen05_kernel(nq, nkv, ps, window):
     torch.testing.assert_close(out.float().cpu(), exp, rtol=2e-2, atol=1e-2)
 
 
+def test_prefill_attention_tcgen05_random_shapes_one_after_another():
+    """Sixty launches of random shapes in a row, each against the mma.sync kernel: fewer blocks than SMs and several
+    times more, rows whose last block is nearly empty, rows of one query, windows, and after each launch the
+    counter that the resident CTAs draw their blocks from must be back at zero for the next one."""
+    import random
+    rng = random.Random(11)
+    hd = 128
+    for case in range(60):
+        nkv = rng.choice([1, 2, 3, 8])
+        nq = nkv * rng.choice([1, 2, 4, 5])
+        ps = rng.choice([16, 32, 64])
+        R = rng.randint(1, 6)
+        q_lens = [rng.choice([1, 2, 17, 128, 255, 256, 257, rng.randint(1, 900)]) for _ in range(R)]
+        lens = [n + rng.choice([0, 0, 5, 128, rng.randint(0, 600)]) for n in q_lens]
+        window = rng.choice([None, None, 33, 128, 300])
+        q, kc, vc, pos, rows, bt, qi, kv = _fast_setup(nq, nkv, hd, ps, lens, q_lens, seed=100 + case)
+        got = torch.full((q.shape[0], nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        want = torch.zeros_like(got)
+        ops.paged_attention_prefill_tc(q, got, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, max(q_lens))
+        ops.paged_attention_prefill(q, want, kc, vc, qi, kv, bt, nq, nkv, hd, ps, 1 / math.sqrt(hd), window, max(q_lens))
+        ops.check_errors(DEV)
+        torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=1e-2,
+                                   msg=lambda m: f"case {case}: nq {nq} nkv {nkv} page {ps} q {q_lens} kv {lens} window {window}: {m}")
+
+
 def test_prefill_attention_tcgen05_sharp_scores_and_stale_rows():
     """Scores far apart (the lazy rescaling of the accumulator must kick in) and a cache
     whose unused slots hold huge values (they must not leak through P = 0)."""
