@@ -44,7 +44,7 @@
 // product with the values waits until they have taken O out of tensor memory).
 // Scores, maxima, sums and the accumulators are float32.  Every mbarrier wait is bounded; when one runs
 // out the kernel raises the error flag, stops, draws the remaining tickets so that the counter ends at
-// zero, frees its TMEM and returns.  One launch at a time uses the counter (launches of one stream).
+// zero, frees its TMEM and returns.
 #include "common.cuh"
 #include "tcgen05_utils.cuh"
 using namespace arle;
@@ -107,15 +107,17 @@ __device__ __forceinline__ void reg_more() { asm volatile("setmaxnreg.inc.sync.a
 template <int N>
 __device__ __forceinline__ void reg_less() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(N)); }
 
-// The blocks of the running launch that were drawn after every CTA's first (which is the block of its own index) (one
-// launch at a time: the launches of a stream follow one another).  Every CTA draws tickets until it draws one beyond the
-// last block; the last ticket of all sets the counter back to zero.
-__device__ unsigned int g_ticket;
+// The blocks of a running launch that were drawn after every CTA's first (which is the block of its own index).  Every
+// CTA draws tickets until it draws one beyond the last block; the last ticket of all sets the counter back to zero.
+// Launches take the counters in turn, so launches that run at the same time (on several streams) do not share one
+// unless more than kTicketSlots of them are under way.
+constexpr int kTicketSlots = 64;
+__device__ unsigned int g_ticket[kTicketSlots];
 
 // Ticket number gridDim.x + (draws before this one); the draw that must be the last of the launch resets the counter.
-__device__ __forceinline__ unsigned int draw_ticket(int nblocks) {
-  const unsigned int raw = atomicAdd(&g_ticket, 1u);
-  if (raw + 1 == (unsigned int)nblocks) atomicExch(&g_ticket, 0u);      // nblocks - grid blocks and grid tickets beyond them
+__device__ __forceinline__ unsigned int draw_ticket(int nblocks, int slot) {
+  const unsigned int raw = atomicAdd(&g_ticket[slot], 1u);
+  if (raw + 1 == (unsigned int)nblocks) atomicExch(&g_ticket[slot], 0u);      // nblocks - grid blocks and grid tickets beyond them
   return raw + gridDim.x;
 }
 
@@ -170,7 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, const int* __restrict__ q_indptr,
     const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride, int bt_width, int nq, int nkv,
-    int page_size, float scale_log2, int window, int skip_single, int nyb, int nblocks, int* __restrict__ err) {
+    int page_size, float scale_log2, int window, int skip_single, int nyb, int nblocks, int ticket_slot, int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ unsigned char smem_dyn[];
@@ -255,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
             b = first_has_queries ? (int)blockIdx.x : -2;
           } else if (it < 2 || mbar_wait_bounded(smem_addr(&work_empty[it & 1]), (uint32_t)(((it >> 1) & 1) ^ 1), aborted)) {
             if (!*aborted) {
-              const unsigned int tk = draw_ticket(nblocks);
+              const unsigned int tk = draw_ticket(nblocks, ticket_slot);
               if (tk < (unsigned int)nblocks) b = (int)tk; else ended = true;
               if (b >= 0 && !work_blk[it & 1].init(b, nq, nkv, nyb, q_indptr, kv_lens, window, skip_single)) b = -2;
             }
@@ -335,7 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
       if (keys && lane == 0 && !ended) {
         // a wait ran out: the tickets are still drawn to the end, so that the counter is back at zero for the next launch
         for (int i = 0; i <= nblocks; ++i)
-          if (draw_ticket(nblocks) >= (unsigned int)nblocks) break;
+          if (draw_ticket(nblocks, ticket_slot) >= (unsigned int)nblocks) break;
       }
       // No copy may still be in flight when the CTA ends.  The issuing thread has waited for every tile
       // unless a wait ran out, so this is free otherwise.
@@ -623,9 +625,11 @@ ARLE_API int arle_paged_attention_prefill_tc(const void* q, int q_row_stride, in
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int ctas = (int)(nblocks < sms ? nblocks : sms);
+  static unsigned int launches = 0;
+  const int ticket_slot = (int)(launches++ % kTicketSlots);
   cudaError_t e = launch_kernel(paged_prefill_tc_kernel, dim3(ctas), dim3(kThreads), smem, s, 1, mq, mk, mv, (__nv_bfloat16*)out,
                                 q_indptr, kv_lens, block_table, bt_stride, bt_width, nq, nkv, page_size,
-                                scale * 1.4426950408889634f, window, skip_single, nyb, (int)nblocks, err);
+                                scale * 1.4426950408889634f, window, skip_single, nyb, (int)nblocks, ticket_slot, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }
