@@ -31,6 +31,9 @@
 // token's new key (the CTA that holds the pair's last tile), whose key and value it stores into the
 // cache and writes over the stale slot of the tile in shared memory before the tile is used.  One
 // launch and one pass over the projection output fewer per layer.
+// The table of the rows, the shares of the CTAs and each CTA's first page ids depend on the step alone, not on the
+// layer: arle_decode_stream_plan writes them out once per step (one block per CTA of the launches to come), and a launch
+// that is given the plan reads it in one round trip to memory instead of working it out in three.
 // Rows whose step entry has more than one token are skipped.  The key range of a row is
 // [max(0, kv_len - window), kv_len).  Every mbarrier wait is bounded: when one runs out the
 // kernel raises the error flag, stops waiting and runs to its end.
@@ -119,13 +122,152 @@ __device__ __forceinline__ void prep_head(const __nv_bfloat16* src, const float*
   }
 }
 
+constexpr int kPlanHeader = 4;               // units, units per CTA, shared out by pair or not, unused
+
+// The rows' table and the CTAs' shares, by all threads of a block (kThreads of them).  prefix [R + 1], kvl [R], tok [R]
+// and the scalars are in shared memory; the scalars own_* are those of CTA `cta`.  Ends with a barrier.
+__device__ __forceinline__ void stream_shares(const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, int R, int nkv,
+                                              int window, int C, int cta, int* prefix, int* kvl, int* tok, int* units_out,
+                                              int* per_out, int* by_pair_out, int* own_row_out, int* own_first_out,
+                                              int* own_k_out) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int r = tid; r < R; r += kThreads) {
+    const int t = q_indptr[r], t_end = q_indptr[r + 1], len = kv_lens[r];     // three loads under way at once, not one after another
+    const bool single = t_end - t == 1;
+    const int kv_len = single ? len : -1;
+    kvl[r] = kv_len;
+    tok[r] = t;
+    int units = 0;
+    if (kv_len > 0) {
+      const int lo = (window > 0 && kv_len > window) ? kv_len - window : 0;
+      units = ((kv_len + kTile - 1) / kTile - lo / kTile) * nkv;
+    }
+    prefix[r + 1] = units;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    if (lane == 0) prefix[0] = 0;
+    for (int base = 0; base < R; base += 32) {
+      const int i = base + lane;
+      int v = i < R ? prefix[i + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      if (i < R) prefix[i + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+
+  const int U = prefix[R];
+  const int per = max(1, (U + C - 1) / C);               // units per CTA
+  if (tid == 0) *units_out = U, *per_out = per;
+  // Two ways of sharing out the units.  Evenly, whatever the pairs are: CTA c takes units
+  // [c * per, (c + 1) * per), and its range may end inside one pair and go on into the next; every such
+  // piece costs a merge and a hand-over.  Or, when there are fewer pairs than CTAs (few rows), by pair:
+  // the pairs of row r get k_r = T_r C / U CTAs each (T_r tiles, rounded down, at least one) and a CTA takes
+  // one piece of one pair, ceil(T_r / k_r) tiles: one merge per CTA, and none handed over when k_r = 1.
+  // By pair is taken when no CTA gets more than 5/4 of an even share.
+  if (warp == 0) {
+    int mine_row = -1, mine_first = 0, mine_k = 0, carry = 0, worst = 0;
+    const bool may = U > 0 && (long long)R * nkv <= C;
+    for (int base = 0; may && base < R; base += 32) {
+      const int i = base + lane;
+      const int T_i = i < R ? (prefix[i + 1] - prefix[i]) / nkv : 0;
+      const int k_i = T_i > 0 ? max(1, (int)((long long)T_i * C / U)) : 0;
+      worst = max(worst, k_i ? (T_i + k_i - 1) / k_i : 0);
+      int v = k_i * nkv;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      const int first = carry + v - k_i * nkv;
+      if (k_i && first <= cta && cta < first + k_i * nkv) mine_row = i, mine_first = first, mine_k = k_i;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) worst = max(worst, __shfl_xor_sync(0xffffffffu, worst, o));
+    const bool take = may && carry <= C && 4 * worst <= 5 * per;
+    if (lane == 0) *by_pair_out = take ? 1 : 0, *own_row_out = -1;
+    __syncwarp();
+    if (take && mine_row >= 0) *own_row_out = mine_row, *own_first_out = mine_first, *own_k_out = mine_k;
+  }
+  __syncthreads();
+}
+
+// The units [u0, u1) of CTA `cta` from the shares (u0 >= u1: none).
+__device__ __forceinline__ void own_units(int cta, int by_pair, int own_row, int own_first, int own_k, const int* prefix, int nkv,
+                                          int U, int per, int& u0, int& u1) {
+  if (by_pair) {
+    if (own_row < 0) {
+      u0 = u1 = 0;
+      return;
+    }
+    const int T = (prefix[own_row + 1] - prefix[own_row]) / nkv;
+    const int rel = cta - own_first;
+    const int kvh = rel / own_k, piece = rel - kvh * own_k;
+    const int tp = (T + own_k - 1) / own_k;
+    const int pair_begin = prefix[own_row] + kvh * T;
+    u0 = pair_begin + piece * tp;
+    u1 = min(pair_begin + T, u0 + tp);
+  } else {
+    u0 = cta * per;
+    u1 = min(U, u0 + per);
+  }
+}
+
+// The plan of a step: what every launch of decode_stream_kernel with these rows, kv heads, window, block table and grid
+// works out before it can ask for its first keys, written out once (one block per CTA of those launches) so that the
+// launches of the step's layers read it instead: one round trip to memory where they made three, one after another.
+// plan: [units, units per CTA, by pair, 0], then (own_row, own_first, own_k) of every CTA, then the first 32 page ids of
+// every CTA's first piece (what its producers would read from the block table first), then prefix [R + 1], kvl [R], tok [R].
+__global__ void __launch_bounds__(kThreads) decode_stream_plan_kernel(const int* __restrict__ q_indptr, const int* __restrict__ kv_lens,
+                                                                      const int* __restrict__ block_table, int bt_stride, int bt_width,
+                                                                      int page_size, int R, int nkv, int window, int* __restrict__ plan) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int rows_s[];                         // prefix [R + 1], kvl [R], tok [R]
+  __shared__ int units, per, by_pair, own_row, own_first, own_k;
+  const int C = (int)gridDim.x, cta = (int)blockIdx.x;
+  stream_shares(q_indptr, kv_lens, R, nkv, window, C, cta, rows_s, rows_s + R + 1, rows_s + 2 * R + 1, &units, &per, &by_pair, &own_row,
+                &own_first, &own_k);
+  const int tid = threadIdx.x;
+  int* triples = plan + kPlanHeader;
+  int* pages = triples + 3 * C;
+  int* rows_out = pages + 32 * C;
+  if (cta == 0) {
+    for (int i = tid; i < 3 * R + 1; i += kThreads) rows_out[i] = rows_s[i];
+    if (tid == 0) plan[0] = units, plan[1] = per, plan[2] = by_pair, plan[3] = 0;
+  }
+  if (tid == 0) triples[3 * cta] = own_row, triples[3 * cta + 1] = own_first, triples[3 * cta + 2] = own_k;
+  if (tid < 32) {
+    int u0, u1, page = 0;
+    own_units(cta, by_pair, own_row, own_first, own_k, rows_s, nkv, units, per, u0, u1);
+    if (u0 < u1) {
+      const Rows rows{rows_s, rows_s + R + 1, R, nkv, window};
+      const int r = rows.row_of(u0);
+      int lo, kv_len, tlo, thi;
+      rows.tiles_of(r, lo, kv_len, tlo, thi);
+      const int tile0 = tlo + (u0 - rows_s[r]) % (thi - tlo);
+      const int p0 = tile0 * kTile / page_size;
+      page = block_table[(size_t)r * bt_stride + min(p0 + tid, bt_width - 1)];
+    }
+    pages[32 * cta + tid] = page;
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     const __nv_bfloat16* __restrict__ q, int q_row_stride, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ q_indptr, const int* __restrict__ kv_lens, const int* __restrict__ block_table, int bt_stride,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int R, int nq, int nkv,
-    int bt_width, int page_size, int ps_shift, float scale_log2, int window, int stages, Prep prep, int* __restrict__ err) {
+    int bt_width, int page_size, int ps_shift, float scale_log2, int window, int stages, Prep prep, const int* __restrict__ plan,
+    int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr uint32_t OPERAND = kTile * HD * 2;            // bytes of the keys (or the values) of one stage
@@ -164,85 +306,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
     const CUtensorMap* m = warp > kConsumerWarps ? &map_v : &map_k;
     asm volatile("prefetch.tensormap [%0];\n" ::"l"(m) : "memory");
   }
-  for (int r = tid; r < R; r += kThreads) {
-    const int t = q_indptr[r], t_end = q_indptr[r + 1], len = kv_lens[r];     // three loads under way at once, not one after another
-    const bool single = t_end - t == 1;
-    const int kv_len = single ? len : -1;
-    kvl[r] = kv_len;
-    tok[r] = t;
-    int units = 0;
-    if (kv_len > 0) {
-      const int lo = (window > 0 && kv_len > window) ? kv_len - window : 0;
-      units = ((kv_len + kTile - 1) / kTile - lo / kTile) * nkv;
+  __shared__ int plan_units, plan_per;
+  int first_pages = 0;                                    // a producer lane's page id of the CTA's first piece (with a plan)
+  if (plan) {
+    // The step's plan (arle_decode_stream_plan): the rows' table and the shares worked out once for all layers
+    const int* rows_plan = plan + kPlanHeader + (3 + 32) * C;
+    for (int i = tid; i < 3 * R + 1; i += kThreads) prefix[i] = rows_plan[i];          // prefix, kvl, tok lie one after the other
+    if (warp >= kConsumerWarps) first_pages = plan[kPlanHeader + 3 * C + 32 * blockIdx.x + lane];
+    if (tid == 0) {
+      plan_units = plan[0], plan_per = plan[1], by_pair = plan[2];
+      own_row = plan[kPlanHeader + 3 * blockIdx.x], own_first = plan[kPlanHeader + 3 * blockIdx.x + 1];
+      own_k = plan[kPlanHeader + 3 * blockIdx.x + 2];
     }
-    prefix[r + 1] = units;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    int carry = 0;
-    if (lane == 0) prefix[0] = 0;
-    for (int base = 0; base < R; base += 32) {
-      const int i = base + lane;
-      int v = i < R ? prefix[i + 1] : 0;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, v, o);
-        if (lane >= o) v += n;
-      }
-      if (i < R) prefix[i + 1] = carry + v;
-      carry += __shfl_sync(0xffffffffu, v, 31);
-    }
-  }
-  __syncthreads();
-
-  const int U = prefix[R];
-  const int per = max(1, (U + C - 1) / C);               // units per CTA
-  // Two ways of sharing out the units.  Evenly, whatever the pairs are: CTA c takes units
-  // [c * per, (c + 1) * per), and its range may end inside one pair and go on into the next; every such
-  // piece costs a merge and a hand-over.  Or, when there are fewer pairs than CTAs (few rows), by pair:
-  // the pairs of row r get k_r = T_r C / U CTAs each (T_r tiles, rounded down, at least one) and a CTA takes
-  // one piece of one pair, ceil(T_r / k_r) tiles: one merge per CTA, and none handed over when k_r = 1.
-  // By pair is taken when no CTA gets more than 5/4 of an even share.
-  if (warp == 0) {
-    int mine_row = -1, mine_first = 0, mine_k = 0, carry = 0, worst = 0;
-    const bool may = U > 0 && (long long)R * nkv <= C;
-    for (int base = 0; may && base < R; base += 32) {
-      const int i = base + lane;
-      const int T_i = i < R ? (prefix[i + 1] - prefix[i]) / nkv : 0;
-      const int k_i = T_i > 0 ? max(1, (int)((long long)T_i * C / U)) : 0;
-      worst = max(worst, k_i ? (T_i + k_i - 1) / k_i : 0);
-      int v = k_i * nkv;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int n = __shfl_up_sync(0xffffffffu, v, o);
-        if (lane >= o) v += n;
-      }
-      const int first = carry + v - k_i * nkv;
-      if (k_i && first <= (int)blockIdx.x && (int)blockIdx.x < first + k_i * nkv) mine_row = i, mine_first = first, mine_k = k_i;
-      carry += __shfl_sync(0xffffffffu, v, 31);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) worst = max(worst, __shfl_xor_sync(0xffffffffu, worst, o));
-    const bool take = may && carry <= C && 4 * worst <= 5 * per;
-    if (lane == 0) by_pair = take ? 1 : 0, own_row = -1;
-    __syncwarp();
-    if (take && mine_row >= 0) own_row = mine_row, own_first = mine_first, own_k = mine_k;
-  }
-  __syncthreads();
-  int u0, u1;
-  if (by_pair) {
-    if (own_row < 0) return;
-    const int T = (prefix[own_row + 1] - prefix[own_row]) / nkv;
-    const int rel = (int)blockIdx.x - own_first;
-    const int kvh = rel / own_k, piece = rel - kvh * own_k;
-    const int tp = (T + own_k - 1) / own_k;
-    const int pair_begin = prefix[own_row] + kvh * T;
-    u0 = pair_begin + piece * tp;
-    u1 = min(pair_begin + T, u0 + tp);
+    __syncthreads();
   } else {
-    u0 = (int)blockIdx.x * per;
-    u1 = min(U, u0 + per);
+    stream_shares(q_indptr, kv_lens, R, nkv, window, C, (int)blockIdx.x, prefix, kvl, tok, &plan_units, &plan_per, &by_pair, &own_row,
+                  &own_first, &own_k);
   }
+  const int U = plan_units;
+  const int per = plan_per;
+  int u0, u1;
+  own_units((int)blockIdx.x, by_pair, own_row, own_first, own_k, prefix, nkv, U, per, u0, u1);
   if (u0 >= u1) return;
   const Rows rows{prefix, kvl, R, nkv, window};
   const volatile int* aborted = &abort_flag;
@@ -273,7 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stream_kernel(
       // Page ids come 32 at a time, one per lane, and a second 32 ahead of them, so that no
       // tile waits for a read of the block table; a lane picks its page with a shuffle.
       int p0 = page_index(tile0 * kTile);
-      int cur = __ldg(bt + min(p0 + lane, bt_width - 1));
+      int cur = (plan && u == u0) ? first_pages : __ldg(bt + min(p0 + lane, bt_width - 1));
       int nxt = __ldg(bt + min(p0 + 32 + lane, bt_width - 1));
       int key0 = tile0 * kTile + c * 16;
       for (int i = 0; i < ntile; ++i) {
@@ -599,7 +683,7 @@ template <int HD>
 int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, int q_row_stride, void* out,
                   const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, float* part_o,
                   float* part_ml, int* counters, int rows, int nq, int nkv, int bt_width, int page_size, float scale, int window,
-                  int ctas, const Prep& prep, int* err, cudaStream_t s) {
+                  int ctas, const Prep& prep, const int* plan, int* err, cudaStream_t s) {
   int ps_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (ps_shift = 0; (1 << ps_shift) < page_size; ++ps_shift) {}
@@ -625,7 +709,7 @@ int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, i
   if (e != cudaSuccess) return (int)e;
   e = launch_kernel(decode_stream_kernel<HD>, dim3(ctas), dim3(kThreads), smem, s, 1, mk, mv, (const __nv_bfloat16*)q,
                     q_row_stride, (__nv_bfloat16*)out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                    rows, nq, nkv, bt_width, page_size, ps_shift, scale * 1.4426950408889634f, window, stages, prep, err);
+                    rows, nq, nkv, bt_width, page_size, ps_shift, scale * 1.4426950408889634f, window, stages, prep, plan, err);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }
@@ -638,7 +722,7 @@ ARLE_API int arle_paged_attention_decode_stream_prep(const void* q, int q_row_st
                                                      float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
                                                      int page_size, float scale, int window, int rows, int ctas, int fused,
                                                      const int* slot_mapping, const float* q_weight, const float* k_weight,
-                                                     float eps, const float* inv_freq, int* err, cudaStream_t s);
+                                                     float eps, const float* inv_freq, const int* plan, int* err, cudaStream_t s);
 
 // k_cache / v_cache: [cache_pages, nkv, page_size, hd].  Scratch: part_o float32
 // [(ctas + rows * nkv) * (nq / nkv) * hd], part_ml float32 [(ctas + rows * nkv) * (nq / nkv) * 2], counters
@@ -654,7 +738,22 @@ ARLE_API int arle_paged_attention_decode_stream(const void* q, int q_row_stride,
   return arle_paged_attention_decode_stream_prep(q, q_row_stride, out, k_cache, v_cache, cache_pages, q_indptr, kv_lens,
                                                  block_table, bt_stride, bt_width, part_o, part_ml, counters, nq, nkv, hd,
                                                  page_size, scale, window, rows, ctas, 0, nullptr, nullptr, nullptr, 0.f, nullptr,
-                                                 err, s);
+                                                 nullptr, err, s);
+}
+
+// Ints of a step's plan for this many rows and CTAs.
+ARLE_API int arle_decode_stream_plan_ints(int rows, int ctas) { return kPlanHeader + (3 + 32) * ctas + 3 * rows + 1; }
+
+// Fills a step's plan (arle_decode_stream_plan_ints(rows, ctas) ints): launches of the streaming kernel with the same
+// q_indptr, kv_lens, block table, page size, rows, nkv, window and ctas that are given it skip their own working out of
+// the shares and their first read of the block table.
+ARLE_API int arle_decode_stream_plan(const int* q_indptr, const int* kv_lens, const int* block_table, int bt_stride, int bt_width,
+                                     int page_size, int rows, int nkv, int window, int ctas, int* plan, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (rows > 2048 || ctas < 1 || ctas > 1024 || nkv <= 0 || page_size <= 0 || bt_width < 1 || !plan || !block_table) return ARLE_E_BADARG;
+  launch_kernel(decode_stream_plan_kernel, dim3(ctas), dim3(kThreads), (size_t)(3 * rows + 1) * sizeof(int), s, 1, q_indptr, kv_lens,
+                block_table, bt_stride, bt_width, page_size, rows, nkv, window, plan);
+  return launch_status();
 }
 
 // The same with the fused preparation (fused != 0): q is the raw projection output of the step's tokens
@@ -668,7 +767,7 @@ ARLE_API int arle_paged_attention_decode_stream_prep(const void* q, int q_row_st
                                                      float* part_o, float* part_ml, int* counters, int nq, int nkv, int hd,
                                                      int page_size, float scale, int window, int rows, int ctas, int fused,
                                                      const int* slot_mapping, const float* q_weight, const float* k_weight,
-                                                     float eps, const float* inv_freq, int* err, cudaStream_t s) {
+                                                     float eps, const float* inv_freq, const int* plan, int* err, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (fused && (!slot_mapping || ((uintptr_t)q & 15) || (q_row_stride % 8) != 0)) return ARLE_E_BADARG;
   const Prep prep{fused ? 1 : 0, slot_mapping, q_weight, k_weight, eps, inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
@@ -687,7 +786,7 @@ ARLE_API int arle_paged_attention_decode_stream_prep(const void* q, int q_row_st
   if (rc) return rc;
   if (hd == 128)
     return launch_stream<128>(mk, mv, q, q_row_stride, out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                              rows, nq, nkv, bt_width, page_size, scale, window, ctas, prep, err, s);
+                              rows, nq, nkv, bt_width, page_size, scale, window, ctas, prep, plan, err, s);
   return launch_stream<64>(mk, mv, q, q_row_stride, out, q_indptr, kv_lens, block_table, bt_stride, part_o, part_ml, counters,
-                           rows, nq, nkv, bt_width, page_size, scale, window, ctas, prep, err, s);
+                           rows, nq, nkv, bt_width, page_size, scale, window, ctas, prep, plan, err, s);
 }

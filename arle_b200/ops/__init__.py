@@ -50,7 +50,9 @@ _SIGNATURES = {
     "arle_paged_attention_decode_stream": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
                                            _F, _I, _I, _I, _P, _P],
     "arle_paged_attention_decode_stream_prep": [_P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I,
-                                                _F, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P],
+                                                _F, _I, _I, _I, _I, _P, _P, _P, _F, _P, _P, _P, _P],
+    "arle_decode_stream_plan_ints": [_I, _I],
+    "arle_decode_stream_plan": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "arle_paged_attention_prefill": [_P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P],
     "arle_paged_attention_prefill_tc": [_P, _I, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                                         _I, _I, _I, _P, _P],
@@ -643,12 +645,28 @@ def decode_attention_with_prep(qkv, out, k_cache, v_cache, slot_mapping, q_weigh
     piece_o = batch.ws.get("attn_piece_o", (slots * hd,), torch.float32)
     piece_ml = batch.ws.get("attn_piece_ml", (slots * 2,), torch.float32)
     counters = batch.ws.get_zeroed("attn_piece_counters", (R * nkv,), torch.int32)
+    # How the keys are shared out among the CTAs, and which pages each CTA reads first, depends on the rows' lengths,
+    # the kv heads, the window and the group's block table alone: worked out by the step's first layer for all that
+    # follow (the step's memo, where there is one)
+    plan = None
+    memo = getattr(batch, "memo", None)
+    if memo is not None:
+        key = ("decode_stream_plan", nkv, int(window) if window else 0, ctas, block_table.data_ptr(), block_table.stride(0),
+               block_table.shape[1], page_size)
+        plan = memo.get(key)
+        if plan is None:
+            n = library().arle_decode_stream_plan_ints(R, int(ctas))
+            plan = batch.ws.get(f"decode_stream_plan_{len(memo)}", (n,), torch.int32)
+            _check(library().arle_decode_stream_plan(_ptr(batch.q_indptr), _ptr(batch.kv_lens), _ptr(block_table),
+                                                     block_table.stride(0), block_table.shape[1], page_size, R, nkv, key[2],
+                                                     int(ctas), _ptr(plan), _stream()), "decode_stream_plan")
+            memo[key] = plan
     _check(library().arle_paged_attention_decode_stream_prep(
         _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(batch.q_indptr),
         _ptr(batch.kv_lens), _ptr(block_table), block_table.stride(0), block_table.shape[1], _ptr(piece_o), _ptr(piece_ml),
         _ptr(counters), nq, nkv, hd, page_size, float(scale), int(window) if window else 0, R, int(ctas), 1,
-        _ptr(slot_mapping), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), _ptr(error_flag(qkv.device)),
-        _stream()), "decode_attention_with_prep")
+        _ptr(slot_mapping), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), _ptr(plan),
+        _ptr(error_flag(qkv.device)), _stream()), "decode_attention_with_prep")
 
 
 def decode_splits(rows: int, nkv: int, kv_bound: int, device=None) -> int:
