@@ -612,6 +612,17 @@ def test_decode_attention_with_fused_preparation(nq, nkv, hd, ps, window, lens, 
         ops.check_errors(DEV)
         assert torch.equal(kc_b, kc_a) and torch.equal(vc_b, vc_a)
         assert torch.equal(got, want)
+    # with the step's plan (shares and first pages worked out once, kept in the step's memo): the same bits, twice
+    # (the second launch finds the plan in the memo)
+    batch.memo = {}
+    kc_c, vc_c = kc.clone(), vc.clone()
+    for _ in range(2):
+        again = torch.full((R, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.decode_attention_with_prep(qkv, again, kc_c, vc_c, slots, qw, kw, eps, inv_freq, bt, nq, nkv, hd, ps,
+                                       1 / math.sqrt(hd), window, batch)
+        ops.check_errors(DEV)
+        assert torch.equal(again, want) and torch.equal(kc_c, kc_a) and torch.equal(vc_c, vc_a)
+    assert len(batch.memo) == 1
 
 
 @pytest.mark.parametrize("ctas", [7, 148])
