@@ -5,7 +5,9 @@
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with every
 request at a 2,048-token context (device time of K decode steps, CUDA events);
-``points`` holds batch 1 and 64; ``prefill`` one 2,048-token prompt; ``roofline``
+``points`` holds batch 1 and 64; ``prefill`` one 2,048-token prompt (``ms``: a single
+step after a pause, as a request meets a waiting GPU; ``ms_in_a_row``: steps that follow
+the decode runs and one another, when the 1 kW power cap has the clocks down); ``roofline``
 the bytes the decode step must read (each weight once + the live requests' cache)
 over its time against the measured copy bandwidth; ``e2e`` the same decode metric
 through ``Engine.generate`` with token ids going in from and coming back to the
