@@ -583,7 +583,9 @@ def test_decode_attention_with_fused_preparation(nq, nkv, hd, ps, window, lens, 
     """One launch that norms and rotates the queries and the new keys, stores the new keys and values and
     attends, against the preparation kernel followed by the attention kernel: the same arithmetic in the
     same order, so the same bits in the output and in the cache (also at the first token of a sequence, at
-    the edges of tiles and pages, and with pieces of several rows in one CTA)."""
+    the edges of tiles and pages, and with pieces of several rows in one CTA).  Without a rotation the separate
+    preparation runs on the general kernel, which adds the squares of a head in another order: equal within
+    rounding there (one draw in twenty of random shapes differs in a bit), bit for bit with the rotation."""
     from types import SimpleNamespace
     from arle_b200.engine import Workspace
 
@@ -610,8 +612,13 @@ def test_decode_attention_with_fused_preparation(nq, nkv, hd, ps, window, lens, 
         ops.decode_attention_with_prep(qkv, got, kc_b, vc_b, slots, qw, kw, eps, inv_freq, bt, nq, nkv, hd, ps,
                                        1 / math.sqrt(hd), window, batch)
         ops.check_errors(DEV)
-        assert torch.equal(kc_b, kc_a) and torch.equal(vc_b, vc_a)
-        assert torch.equal(got, want)
+        if rot:
+            assert torch.equal(kc_b, kc_a) and torch.equal(vc_b, vc_a)
+            assert torch.equal(got, want)
+        else:
+            torch.testing.assert_close(kc_b.float(), kc_a.float(), rtol=1e-2, atol=1e-2)
+            torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=1e-2)
+            assert torch.equal(vc_b, vc_a)
     # with the step's plan (shares and first pages worked out once, kept in the step's memo): the same bits, twice
     # (the second launch finds the plan in the memo)
     batch.memo = {}
@@ -621,7 +628,7 @@ def test_decode_attention_with_fused_preparation(nq, nkv, hd, ps, window, lens, 
         ops.decode_attention_with_prep(qkv, again, kc_c, vc_c, slots, qw, kw, eps, inv_freq, bt, nq, nkv, hd, ps,
                                        1 / math.sqrt(hd), window, batch)
         ops.check_errors(DEV)
-        assert torch.equal(again, want) and torch.equal(kc_c, kc_a) and torch.equal(vc_c, vc_a)
+        assert torch.equal(again, got) and torch.equal(kc_c, kc_b) and torch.equal(vc_c, vc_b)
     assert len(batch.memo) == 1
 
 
