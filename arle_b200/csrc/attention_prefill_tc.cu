@@ -269,6 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
         }
         __syncwarp();
         const int b = __shfl_sync(0xffffffffu, lane == 0 ? wait_ticket(it) : 0, 0);
+        __syncwarp();                                       // the first lane's wait orders the other lanes' reads of the slot
         Block blk;
         if (b >= 0) blk = work_blk[it & 1];
         __syncwarp();
@@ -452,6 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_prefill_tc_kernel(
     for (int it = 0; ok; ++it) {
       int b = lane == 0 ? wait_ticket(it) : 0;
       b = __shfl_sync(0xffffffffu, b, 0);
+      __syncwarp();                                         // the first lane's wait orders the other lanes' reads of the slot
       Block blk;
       if (b >= 0) blk = work_blk[it & 1];
       __syncwarp();
