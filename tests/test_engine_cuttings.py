@@ -178,3 +178,26 @@ def test_graph_table_width_never_exceeds_the_host_table(tmp_path_factory, cpu_ke
     small = ModelRunner(model, 4, 64, 2, max_tokens_per_request=20, device="cpu")        # 5 columns
     small._graphs, small._max_graph_rows = {}, 8
     assert small._graph_key([StepEntry("y", [3], (0,))], [2]) == (1, 5)
+
+
+def test_a_step_starts_with_an_empty_memo(tmp_path_factory, cpu_kernels):
+    """What parts keep in ``ctx.memo`` (tables derived from a step's positions or lengths) belongs to one pass over
+    one step: building the next step empties it, and so does every pass that the runner starts."""
+    from arle_b200.engine import StepContext, StepEntry, Workspace
+    from arle_b200.engine.runner import _forward
+
+    d, reqs, oracle = model_and_oracle("A", tmp_path_factory)
+    model = load_model(d, torch.float32, "cpu")
+    runner = ModelRunner(model, 4, 64, 2, device="cpu")
+    toks = reqs["r3"]
+    runner.cache.add_request("x")
+    runner.cache.append([("x", 5)])
+    ctx = StepContext(runner.cache, Workspace("cpu")).build([StepEntry("x", toks[:5], (4,))], [0])
+    ctx.memo["left over"] = 1
+    logits = _forward(model, ctx)
+    assert "left over" not in ctx.memo
+    assert (logits[0].double() - oracle["r3"][4]).abs().max().item() <= ATOL[torch.float32]
+    ctx.memo["left over"] = 2
+    runner.cache.append([("x", 1)])
+    ctx.build([StepEntry("x", toks[5:6], (0,))], [5])
+    assert ctx.memo == {}
