@@ -413,6 +413,33 @@ def main() -> int:
             for b in (1, 8, 64):
                 m, _, _ = decode_run(b, steps_m, args.warmup, runner=r, sampler=smp, context=ctx_len)
                 more[f"{name}_decode_b{b}_ctx{ctx_len}"] = round(b * 1000.0 / m, 1)
+            if name == "32b":
+                # a 2,048-token prompt as four portions of 512 beside eight requests that decode at a 2,048-token
+                # context: four mixed steps, the median of five such prompts
+                rids = [f"mix-{i}" for i in range(8)]
+                for q in rids:
+                    r.add_request(q)
+                r.cache.append([(q, ctx_len) for q in rids])
+                times = []
+                for rep in range(8):
+                    ids = torch.randint(0, mdl.spec.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
+                    r.add_request(f"mixp-{rep}")
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for part in range(4):
+                        toks = ids[part * 512:(part + 1) * 512]
+                        r.step([StepEntry(q, [7], (0,)) for q in rids] + [StepEntry(f"mixp-{rep}", toks, (511,) if part == 3 else ())])
+                    e1.record()
+                    torch.cuda.synchronize()
+                    r.end_request(f"mixp-{rep}")
+                    if rep >= 3:
+                        times.append(e0.elapsed_time(e1))
+                for q in rids:
+                    r.end_request(q)
+                t_mixed = sorted(times)[len(times) // 2]
+                more["32b_prefill_4x512_beside_8_decodes_tok_s"] = round(PREFILL_TOKENS * 1000.0 / t_mixed, 1)
+                more["32b_mixed_step_ms"] = round(t_mixed / 4, 3)
             del r, smp, mdl
             gc.collect()
             torch.cuda.empty_cache()
