@@ -113,6 +113,7 @@ def gemm_table(args, sizes, torch, ops) -> int:
         for i in range(3):
             fn(i)
         torch.cuda.synchronize()
+        time.sleep(0.25)            # every kernel starts from a GPU at rest: in a row, the later ones would run under the power cap
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(steps):
