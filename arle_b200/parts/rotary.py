@@ -1,8 +1,9 @@
 """Rotary position encoding, half-split pairing, over the first ``rotary_dim``
 elements of a head: inv_freq_i = theta^(-2i/rotary_dim), angle = position *
 inv_freq_i (infer/src/weight_loader.rs:955-989).  The reference tabulates cos and
-sin in bfloat16; here the kernel evaluates sincosf of the float32 angle, so no
-table and no limit on the position."""
+sin of every position in bfloat16; here the kernels evaluate sincosf of the float32
+angle of the positions they meet (for prompt portions once per step, into a table
+that the step's layers share), so there is no limit on the position."""
 from __future__ import annotations
 
 from dataclasses import dataclass
