@@ -12,6 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Sequence, Union
 
+import numpy as np
 import torch
 
 from ..sampling import Sampler, SamplingParams, request_rng
@@ -119,9 +120,10 @@ class Engine:
         rid = request_id if request_id is not None else f"req-{self._next_id}"
         self._next_id += 1
         vocab = self.model.spec.vocab_size
-        for t in prompt:
-            if not 0 <= int(t) < vocab:
-                raise ValueError(f"token id {t} is outside the vocabulary [0, {vocab})")
+        ids = np.asarray(prompt, dtype=np.int64)
+        if ids.size and (ids.min() < 0 or ids.max() >= vocab):
+            t = int(ids[(ids < 0) | (ids >= vocab)][0])
+            raise ValueError(f"token id {t} is outside the vocabulary [0, {vocab})")
         req = self.scheduler.add_request(rid, prompt, params)
         self._rngs[rid] = request_rng(self.options.seed, req.number, req.params)
         return req

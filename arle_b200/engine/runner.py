@@ -16,6 +16,7 @@ from __future__ import annotations
 import gc
 from typing import List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -101,9 +102,10 @@ class ModelRunner:
                 self.cache.add_request(e.request)
             if len(e.tokens) == 1 and int(e.tokens[0]) < 0:
                 continue                            # the token this request sampled last, still on the device
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab:
-                    raise ValueError(f"request {e.request!r}: token id {t} is outside the vocabulary [0, {vocab})")
+            ids = np.asarray(e.tokens, dtype=np.int64)
+            if ids.size and (ids.min() < 0 or ids.max() >= vocab):
+                t = int(ids[(ids < 0) | (ids >= vocab)][0])
+                raise ValueError(f"request {e.request!r}: token id {t} is outside the vocabulary [0, {vocab})")
         starts = [self.cache.num_tokens(e.request) for e in entries]
         self.cache.append([(e.request, len(e.tokens)) for e in entries])
         try:

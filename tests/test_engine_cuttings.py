@@ -201,3 +201,22 @@ def test_a_step_starts_with_an_empty_memo(tmp_path_factory, cpu_kernels):
     runner.cache.append([("x", 1)])
     ctx.build([StepEntry("x", toks[5:6], (0,))], [5])
     assert ctx.memo == {}
+
+
+def test_token_ids_outside_the_vocabulary_are_refused_before_anything_changes(tmp_path_factory, cpu_kernels):
+    from arle_b200 import Engine
+    from arle_b200.engine import StepEntry
+
+    d, reqs, oracle = model_and_oracle("A", tmp_path_factory)
+    vocab = CONFIGS["A"]["vocab_size"]
+    model = load_model(d, torch.float32, "cpu")
+    runner = ModelRunner(model, 4, 16, 2, device="cpu")
+    for bad in ([3, vocab, 5], [3, -1, 5], [vocab + 7]):
+        with pytest.raises(ValueError, match="outside the vocabulary"):
+            runner.step([StepEntry("x", bad, ())])
+        assert runner.cache.num_tokens("x") == 0 and all(g.pool.num_free == g.pool.num_pages for g in runner.cache.groups)
+    eng = Engine(d, dtype="float32", device="cpu", page_size=4, num_pages=16, num_slots=2)
+    with pytest.raises(ValueError, match=f"token id {vocab} is outside the vocabulary"):
+        eng.add_request([1, 2, vocab])
+    with pytest.raises(ValueError, match="token id -4 is outside the vocabulary"):
+        eng.add_request([1, -4])
