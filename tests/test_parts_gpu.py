@@ -126,7 +126,7 @@ def test_first_tokens_of_a_sequence(name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["B", "D", "E"])
+@pytest.mark.parametrize("name", ["B", "D", "E", "F"])
 def test_a_far_token_decides_the_logits(name, dtype, tmp_path):
     """Random weights make attention nearly uniform, which hides a lost page or a wrong
     position.  Here the q and k projections of layer 0 are scaled up so that attention

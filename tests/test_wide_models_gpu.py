@@ -84,3 +84,43 @@ def test_random_model_on_the_device_is_the_model_the_folder_holds(tmp_path_facto
         assert torch.equal(x.mixer.w_qkv, y.mixer.w_qkv) and torch.equal(x.mixer.w_o, y.mixer.w_o)
         assert torch.equal(x.mixer.q_norm, y.mixer.q_norm) and torch.equal(x.ffn.w_gate_up, y.ffn.w_gate_up)
         assert torch.equal(x.ffn.w_down, y.ffn.w_down) and torch.equal(x.mixer_norm.weight, y.mixer_norm.weight)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_a_far_token_decides_the_logits_at_8b_widths(dtype, tmp_path):
+    """Random weights make attention nearly uniform, which hides a lost page or a wrong position.  Here the gain of
+    layer 0's query norm is tripled, so that its attention is sharp, on two layers of Qwen3-8B's widths; a sequence of
+    330 tokens is cut into portions and decoded tokens (tensor-core prefill, the streaming decode kernel with its
+    own preparation, the gated weight-streaming product) and must agree with the plain model, whose late logits
+    depend on single early tokens."""
+    from arle_b200.engine import StepEntry
+    from arle_b200.weights.safetensors_io import SafetensorsFile, write_safetensors
+
+    d = str(tmp_path / "sharp8b")
+    write_random_model(d, WIDE["8b"], seed=5, sigma=0.02, gain_jitter=0.1, device="cuda")
+    path = d + "/model.safetensors"
+    f = SafetensorsFile(path)
+    t = {n: f.tensor(n).clone() for n in f.names()}
+    name = "model.layers.0.self_attn.q_norm.weight"
+    t[name] = (t[name].float() * 3).to(t[name].dtype)
+    write_safetensors(path, t)
+    del t, f
+    cfg, w = plain.read_config(d), plain.read_weights(d)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, cfg["vocab_size"], (330,), generator=g).tolist()
+    want = plain.forward(w, cfg, toks)
+    moved = list(toks)
+    moved[5] = (moved[5] + 1) % cfg["vocab_size"]
+    assert (plain.forward(w, cfg, moved)[-1] - want[-1]).abs().max() > 1e-3      # the last logits see token 5
+    tol = REL_F32 * float(want.std()) if dtype == torch.float32 else \
+        1.5 * (plain.forward(w, cfg, toks, rnd=plain.bf16_round) - want).abs().max().item()
+    del w
+    runner = ModelRunner(load_model(d, dtype, "cuda"), 16, 48, 2)
+    got, at = [], 0
+    for n in (130, 1, 1, 64, 2, 99, 1, 1) + (1,) * 31:
+        got.append(runner.step([StepEntry("r", toks[at:at + n], range(n))]).clone())
+        at += n
+    assert at == 330
+    err = (torch.cat(got).double().cpu() - want).abs().max(dim=1).values
+    bad = (err > tol).nonzero()
+    assert bad.numel() == 0, f"first wrong position {int(bad[0])}: error {err.max().item():.3g}, allowed {tol:.3g}"
